@@ -1,0 +1,51 @@
+"""Build libfp8mm_b200.so in-tree with nvcc for sm_100a.
+
+    python -m fp8_gemm_h20_b200.build [--force] [--verbose]
+
+Cross-compiles without a GPU.  The library is the product's only native code; it has
+no torch dependency and is loaded through ctypes (fp8_gemm_h20_b200/_lib.py).
+"""
+import argparse
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+SOURCES = [PKG / "csrc" / "fp8mm_b200.cu"]
+HEADERS = [PKG / "csrc" / "fp8mm_kernel.cuh", PKG / "csrc" / "ptx_sm100.cuh",
+           PKG.parent / "include" / "fp8mm_b200.h"]
+OUT = PKG / "libfp8mm_b200.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC",
+]
+
+
+def up_to_date():
+    if not OUT.is_file():
+        return False
+    t = OUT.stat().st_mtime
+    return all(p.stat().st_mtime <= t for p in SOURCES + HEADERS + [Path(__file__)])
+
+
+def build(force=False, verbose=False):
+    if not force and up_to_date():
+        return OUT
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", str(OUT), *map(str, SOURCES)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode:
+        raise RuntimeError(f"nvcc failed ({res.returncode}): {' '.join(cmd)}")
+    return OUT
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--verbose", action="store_true")
+    a = ap.parse_args()
+    print(build(a.force, a.verbose))

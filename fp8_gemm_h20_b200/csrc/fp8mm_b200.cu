@@ -1,0 +1,338 @@
+// Host side of the C ABI declared in include/fp8mm_b200.h: legality checks, split
+// legalisation, workspace layout, TMA tensor-map cache and the kernel launch.
+// Replaces the reference's per-kernel Python wrappers (fp8_gemm_h20/kernels/kernel_v2.py:339-376
+// and siblings).  No torch, no allocation, no synchronisation on the launch path.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+#include "../../include/fp8mm_b200.h"
+#include "fp8mm_kernel.cuh"
+
+namespace fp8mm {
+namespace {
+
+constexpr size_t kStatusBytes = 256;         // status words at the head of the workspace
+constexpr size_t kMaxDynSmem = 232448;       // 227 KB opt-in dynamic shared memory per CTA
+constexpr int kMaxDevices = 64;
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct Geometry {
+  int umma_n;       // UMMA N = columns of the accumulator tile
+  bool swap;
+  int tt, wt;       // token / weight tile
+  int t_tiles, w_tiles, tiles;
+  int kb_total, split, kbn;
+  int stages;
+  int threads;
+  size_t smem;
+  size_t counter_bytes, partial_bytes;
+};
+
+bool is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
+
+int check_cfg(int M, int N, int K, const fp8mm_cfg* c) {
+  if (c == nullptr) return FP8MM_E_NULL;
+  if (M < 1 || N < 128 || K < 128 || (N % 128) != 0 || (K % 128) != 0) return FP8MM_E_SHAPE;
+  if (c->flags != 0) return FP8MM_E_CONFIG;
+  if (c->split < 1 || c->group_m < 1 || c->stages < 0 || c->max_ctas < 0) return FP8MM_E_CONFIG;
+  if (c->impl == FP8MM_IMPL_UMMA) {
+    if (c->block_t != 128) return FP8MM_E_CONFIG;
+    if (c->block_w != 128 && c->block_w != 256) return FP8MM_E_CONFIG;
+  } else if (c->impl == FP8MM_IMPL_UMMA_SWAP) {
+    if (c->block_w != 128) return FP8MM_E_CONFIG;
+    if (!is_pow2(c->block_t) || c->block_t < 16 || c->block_t > 256) return FP8MM_E_CONFIG;
+  } else {
+    return FP8MM_E_CONFIG;
+  }
+  return FP8MM_OK;
+}
+
+// Tile counts, legalised split, ring depth and shared-memory size for one call.
+int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
+  const int rc = check_cfg(M, N, K, c);
+  if (rc != FP8MM_OK) return rc;
+  g->swap = c->impl == FP8MM_IMPL_UMMA_SWAP;
+  g->umma_n = g->swap ? c->block_t : c->block_w;
+  g->tt = c->block_t;
+  g->wt = c->block_w;
+  g->t_tiles = (M + g->tt - 1) / g->tt;
+  g->w_tiles = (N + g->wt - 1) / g->wt;
+  g->tiles = g->t_tiles * g->w_tiles;
+  g->kb_total = K / 128;
+  // A split that does not divide the K-block count runs unsplit (kernel_v2.py:355-356).
+  g->split = (c->split > 1 && g->kb_total % c->split == 0) ? c->split : 1;
+  g->kbn = g->kb_total / g->split;
+  const int npw = g->umma_n == 256 ? 8 : 4;
+  g->threads = kProducerThreads + npw * 32;
+  const size_t stage_bytes = 128 * 128 + (size_t)g->umma_n * 128;
+  const size_t tab_bytes = 2 * (size_t)g->kbn * g->tt * sizeof(float) + 2 * (size_t)g->kbn * 2 * sizeof(float);
+  const size_t fixed = 1024 + tab_bytes + sizeof(SharedCtl);
+  if (fixed + 2 * stage_bytes > kMaxDynSmem) return FP8MM_E_CONFIG;
+  int stages = c->stages > 0 ? c->stages : 4;
+  const int fit = (int)((kMaxDynSmem - fixed) / stage_bytes);
+  if (stages > fit) stages = fit;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return FP8MM_E_CONFIG;
+  g->stages = stages;
+  size_t smem = fixed + stages * stage_bytes;
+  // Shared memory share >= TMEM share, so that CTAs that fit on an SM together (this
+  // kernel's or another stream's) can never ask for more than the 512 TMEM columns.
+  const size_t tmem_cols = 2 * g->umma_n < 32 ? 32 : 2 * g->umma_n;
+  const size_t floor_smem = tmem_cols * 456 - 1024;  // (smem + 1 KB reserved) / 228 KB >= cols / 512
+  if (smem < floor_smem) smem = floor_smem;
+  g->smem = smem;
+  g->counter_bytes = g->split > 1 ? align_up((size_t)g->tiles * sizeof(int), 256) : 0;
+  g->partial_bytes = g->split > 1 ? (size_t)g->tiles * g->split * g->umma_n * 128 * sizeof(float) : 0;
+  return FP8MM_OK;
+}
+
+// ------------------------------------------------------------ tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  int rows, k, box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h ^= (size_t)k.rows * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h ^= (size_t)k.k * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
+    h ^= (size_t)k.box_rows * 0x165667B19E3779F9ull + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+
+std::mutex g_mu;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+// Row-major [rows, k] bytes, box = box_rows x 128 bytes, 128-byte swizzle, zero fill
+// outside the tensor.  The encoding depends only on (pointer, shape, box): cached.
+int get_tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* out) {
+  const MapKey key{ptr, rows, k, box_rows};
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+      *out = it->second;
+      return FP8MM_OK;
+    }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return FP8MM_E_DRIVER;
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k};
+  cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUtensorMap m;
+  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides,
+                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return FP8MM_E_DRIVER;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_maps.size() > 8192) g_maps.clear();
+    g_maps.emplace(key, m);
+  }
+  *out = m;
+  return FP8MM_OK;
+}
+
+// ----------------------------------------------------------------- launch
+struct DeviceInfo {
+  int sms = 0;
+  bool attr_set[32] = {};
+};
+DeviceInfo g_dev[kMaxDevices];
+
+unsigned long long timeout_ns() {
+  static unsigned long long v = []() {
+    const char* e = getenv("FP8MM_TIMEOUT_MS");
+    unsigned long long ms = e ? strtoull(e, nullptr, 10) : 2000ull;
+    if (ms < 1) ms = 1;
+    return ms * 1000000ull;
+  }();
+  return v;
+}
+
+template <int UMMA_N, bool SWAP, bool SPLITK>
+int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
+           const KParams& p, int grid, cudaStream_t stream) {
+  auto kern = fp8mm_umma_kernel<UMMA_N, SWAP, SPLITK>;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_dev[dev].attr_set[slot]) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem) !=
+          cudaSuccess)
+        return FP8MM_E_LAUNCH;
+      g_dev[dev].attr_set[slot] = true;
+    }
+  }
+  kern<<<grid, g.threads, g.smem, stream>>>(tm_tok, tm_wgt, p);
+  return cudaGetLastError() == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
+}
+
+template <int UMMA_N, bool SWAP>
+int launch(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
+           const KParams& p, int grid, cudaStream_t stream) {
+  if (g.split > 1) return launch_one<UMMA_N, SWAP, true>(2 * slot + 1, dev, g, tm_tok, tm_wgt, p, grid, stream);
+  return launch_one<UMMA_N, SWAP, false>(2 * slot, dev, g, tm_tok, tm_wgt, p, grid, stream);
+}
+
+}  // namespace
+}  // namespace fp8mm
+
+using namespace fp8mm;
+
+extern "C" {
+
+int fp8mm_b200_version(void) { return 1000; }
+
+const char* fp8mm_b200_strerror(int code) {
+  switch (code) {
+    case FP8MM_OK: return "ok";
+    case FP8MM_E_NULL: return "a required pointer is NULL";
+    case FP8MM_E_SHAPE: return "M must be >= 1 and N, K multiples of 128";
+    case FP8MM_E_CONFIG: return "illegal tile/split/stage configuration";
+    case FP8MM_E_WORKSPACE: return "workspace missing or too small";
+    case FP8MM_E_ALIGN: return "A, B and C must be 16-byte aligned and ldc a multiple of 8";
+    case FP8MM_E_DRIVER: return "CUDA driver call failed (tensor map encode)";
+    case FP8MM_E_LAUNCH: return "kernel launch failed";
+    case FP8MM_E_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    default: return "unknown error";
+  }
+}
+
+int fp8mm_b200_validate(int32_t M, int32_t N, int32_t K, const fp8mm_cfg* cfg) {
+  Geometry g;
+  return make_geometry(M, N, K, cfg, &g);
+}
+
+size_t fp8mm_b200_workspace_bytes(int32_t M, int32_t N, int32_t K, const fp8mm_cfg* cfg) {
+  Geometry g;
+  if (make_geometry(M, N, K, cfg, &g) != FP8MM_OK) return 0;
+  return kStatusBytes + g.counter_bytes + g.partial_bytes;
+}
+
+int fp8mm_b200_workspace_init(void* workspace, size_t ws_bytes, void* stream) {
+  if (workspace == nullptr) return FP8MM_E_NULL;
+  return cudaMemsetAsync(workspace, 0, ws_bytes, static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? FP8MM_OK
+             : FP8MM_E_DRIVER;
+}
+
+int fp8mm_b200_last_status(const void* workspace, int32_t* detail) {
+  if (workspace == nullptr) return FP8MM_E_NULL;
+  int32_t v = 0;
+  if (cudaMemcpy(&v, workspace, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return FP8MM_E_DRIVER;
+  if (detail != nullptr) *detail = v;
+  return v == 0 ? FP8MM_OK : FP8MM_E_DEVICE_TIMEOUT;
+}
+
+int fp8mm_b200_gemm(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace, size_t ws_bytes,
+                    void* stream_) {
+  if (a == nullptr || cfg == nullptr) return FP8MM_E_NULL;
+  if (a->A == nullptr || a->B == nullptr || a->As == nullptr || a->Bs == nullptr || a->C == nullptr)
+    return FP8MM_E_NULL;
+  Geometry g;
+  int rc = make_geometry(a->M, a->N, a->K, cfg, &g);
+  if (rc != FP8MM_OK) return rc;
+  if ((reinterpret_cast<uintptr_t>(a->A) & 15) || (reinterpret_cast<uintptr_t>(a->B) & 15) ||
+      (reinterpret_cast<uintptr_t>(a->C) & 15) || a->ldc < a->N || (a->ldc % 8) != 0)
+    return FP8MM_E_ALIGN;
+  const size_t need = kStatusBytes + g.counter_bytes + g.partial_bytes;
+  if (g.split > 1 && (workspace == nullptr || ws_bytes < need)) return FP8MM_E_WORKSPACE;
+  if (workspace != nullptr && ws_bytes < kStatusBytes) return FP8MM_E_WORKSPACE;
+
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FP8MM_E_DRIVER;
+  if (g_dev[dev].sms == 0) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+      return FP8MM_E_DRIVER;
+    g_dev[dev].sms = sms;
+  }
+
+  CUtensorMap tm_tok, tm_wgt;
+  rc = get_tensor_map(a->A, a->M, a->K, g.swap ? g.umma_n : 128, &tm_tok);
+  if (rc != FP8MM_OK) return rc;
+  rc = get_tensor_map(a->B, a->N, a->K, g.swap ? 128 : g.umma_n, &tm_wgt);
+  if (rc != FP8MM_OK) return rc;
+
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  KParams p;
+  p.As = a->As;
+  p.Bs = a->Bs;
+  p.C = static_cast<__nv_bfloat16*>(a->C);
+  p.status = reinterpret_cast<int*>(ws);
+  p.ws_counter = g.split > 1 ? reinterpret_cast<int*>(ws + kStatusBytes) : nullptr;
+  p.ws_partial = g.split > 1 ? reinterpret_cast<float*>(ws + kStatusBytes + g.counter_bytes) : nullptr;
+  p.as_sm = a->as_stride_m;
+  p.as_sk = a->as_stride_k;
+  p.bs_sn = a->bs_stride_n;
+  p.bs_sk = a->bs_stride_k;
+  p.ldc = a->ldc;
+  p.timeout_ns = timeout_ns();
+  p.M = a->M;
+  p.N = a->N;
+  p.K = a->K;
+  p.kb_per_unit = g.kbn;
+  p.split = g.split;
+  p.t_tiles = g.t_tiles;
+  p.w_tiles = g.w_tiles;
+  p.num_units = g.tiles * g.split;
+  p.group_m = cfg->group_m;
+  p.stages = g.stages;
+
+  // One CTA per SM unless the shared-memory footprint lets two share an SM.
+  int per_sm = (int)((kMaxDynSmem + 1024) / (g.smem + 1024));
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 2) per_sm = 2;
+  int grid = g_dev[dev].sms * per_sm;
+  if (cfg->max_ctas > 0 && grid > cfg->max_ctas) grid = cfg->max_ctas;
+  if (grid > p.num_units) grid = p.num_units;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (g.swap) {
+    switch (g.umma_n) {
+      case 16: return launch<16, true>(0, dev, g, tm_tok, tm_wgt, p, grid, stream);
+      case 32: return launch<32, true>(1, dev, g, tm_tok, tm_wgt, p, grid, stream);
+      case 64: return launch<64, true>(2, dev, g, tm_tok, tm_wgt, p, grid, stream);
+      case 128: return launch<128, true>(3, dev, g, tm_tok, tm_wgt, p, grid, stream);
+      case 256: return launch<256, true>(4, dev, g, tm_tok, tm_wgt, p, grid, stream);
+    }
+  } else {
+    switch (g.umma_n) {
+      case 128: return launch<128, false>(5, dev, g, tm_tok, tm_wgt, p, grid, stream);
+      case 256: return launch<256, false>(6, dev, g, tm_tok, tm_wgt, p, grid, stream);
+    }
+  }
+  return FP8MM_E_CONFIG;
+}
+
+}  // extern "C"

@@ -1,0 +1,442 @@
+// Warp-specialised block-scaled FP8 GEMM for sm_100a.
+//
+//   C[m,n] = sum_kb ( A[m, 128kb..] . B[n, 128kb..] ) * As[m,kb] * Bs[n/128,kb]      (bf16 out)
+//
+// One CTA owns one SM and walks a list of work units (output tile x K-split).
+// Roles, by warp:
+//   warp 0      TMA producer   – streams 128-byte-wide operand tiles into a shared-memory ring
+//   warp 1      MMA issuer     – per 128-wide K block: four tcgen05.mma (K=32 each) into one of
+//                                two TMEM accumulator buffers, fresh accumulator every block
+//   warps 2-3   scale loader   – stages the activation/weight scales of the unit in shared memory
+//   warps 4..   promotion      – tcgen05.ld the finished K block, acc += d * (As*Bs) in FP32
+//                                registers, release the TMEM buffer, finally write bf16 (or the
+//                                split-K partial) to global memory
+// Promotion of K block k overlaps the MMA of block k+1 through the two TMEM buffers.
+//
+// The 128 UMMA rows (= TMEM lanes) carry tokens (SWAP=false) or weight rows (SWAP=true, for
+// small token counts); the UMMA-N columns carry the other operand.  The math follows the
+// reference kernels: fresh accumulator per K block, one scale product per row/column,
+// FP32 promote (fp8_gemm_h20/kernels/kernel_v2.py:77-91,164-174), bf16 store or
+// fixed-order split-K fix-up through a workspace and a self-resetting counter
+// (kernel_v2.py:268-291).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include "ptx_sm100.cuh"
+
+namespace fp8mm {
+
+constexpr int kMaxStages = 12;
+constexpr int kProducerThreads = 128;  // warps 0-3
+
+struct KParams {
+  const float* As;
+  const float* Bs;
+  __nv_bfloat16* C;
+  float* ws_partial;   // [tile][split][UMMA_N][128] fp32, split > 1 only
+  int* ws_counter;     // [tile], zero between launches
+  int* status;         // first word: 0 or the code of the wait that gave up
+  long long as_sm, as_sk, bs_sn, bs_sk, ldc;
+  unsigned long long timeout_ns;
+  int M, N, K;
+  int kb_per_unit;     // K blocks per work unit = (K/128)/split
+  int split;
+  int t_tiles, w_tiles;
+  int num_units;       // t_tiles * w_tiles * split
+  int group_m;
+  int stages;
+};
+
+struct __align__(8) SharedCtl {
+  unsigned long long full[kMaxStages];
+  unsigned long long empty[kMaxStages];
+  unsigned long long tfull[2];
+  unsigned long long tempty[2];
+  unsigned long long scfull[2];
+  unsigned long long scempty[2];
+  unsigned int tmem_base;
+  int abort;
+  int last;
+  int pad;
+};
+
+// Codes written to the status word when a wait runs out (role * 16 + barrier kind).
+enum : int {
+  kWaitProducerEmpty = 0x11,
+  kWaitMmaFull = 0x21,
+  kWaitMmaTmemEmpty = 0x22,
+  kWaitLoaderEmpty = 0x31,
+  kWaitPromoScale = 0x41,
+  kWaitPromoTmemFull = 0x42,
+};
+
+struct BoundedWait {
+  volatile int* abort;
+  int* status;
+  unsigned long long limit_ns;
+  // Wait for the phase with the given parity.  Gives up after limit_ns (or as soon as
+  // another role has given up), records why, and returns false; the caller then leaves
+  // its loop so that the CTA can free its TMEM and exit.
+  __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, int code) const {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0 = 0;
+    unsigned int it = 0;
+    while (true) {
+      if (ptx::mbar_try_wait(bar, parity)) return true;
+      if ((++it & 63u) == 0u) {
+        if (*abort) return false;
+        unsigned long long now = ptx::globaltimer_ns();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > limit_ns) {
+          *abort = 1;
+          if (status != nullptr) atomicCAS(status, 0, code);
+          return false;
+        }
+      }
+    }
+  }
+};
+
+struct UnitCoord {
+  int tile, ti, wi, s;
+};
+
+// Work unit -> (token tile, weight tile, K split).  Tiles are rastered in groups of
+// group_m token tiles with the token index fastest, so CTAs that run at the same time
+// share weight tiles in L2 (the GROUP_SIZE_M raster of kernel_v2.py:125-134).
+__device__ __forceinline__ UnitCoord decode_unit(int u, const KParams& p) {
+  UnitCoord c;
+  c.s = u % p.split;
+  c.tile = u / p.split;
+  const int per_group = p.group_m * p.w_tiles;
+  const int g = c.tile / per_group;
+  const int first_t = g * p.group_m;
+  const int gsz = min(p.t_tiles - first_t, p.group_m);
+  const int r = c.tile - g * per_group;
+  c.ti = first_t + r % gsz;
+  c.wi = r / gsz;
+  return c;
+}
+
+template <int UMMA_N, bool SWAP>
+struct KernelTraits {
+  static constexpr int NPW = UMMA_N == 256 ? 8 : 4;           // promotion warps
+  static constexpr int CPT = UMMA_N / (NPW / 4);              // accumulator columns per thread
+  static constexpr int CH = CPT >= 32 ? 32 : 16;              // columns per tcgen05.ld
+  static constexpr int NCH = CPT / CH;
+  static constexpr int TT = SWAP ? UMMA_N : 128;              // token tile
+  static constexpr int WT = SWAP ? 128 : UMMA_N;              // weight tile
+  static constexpr int THREADS = kProducerThreads + NPW * 32;
+  static constexpr uint32_t ROW_BYTES = 128u * 128u;
+  static constexpr uint32_t COL_BYTES = UMMA_N * 128u;
+  static constexpr uint32_t STAGE_BYTES = ROW_BYTES + COL_BYTES;
+  static constexpr uint32_t TMEM_COLS = 2 * UMMA_N < 32 ? 32 : 2 * UMMA_N;
+  static_assert(SWAP || UMMA_N >= 128, "token-major tiles carry 128 or 256 weight rows");
+};
+
+template <int UMMA_N, bool SWAP, bool SPLITK>
+__global__ void __launch_bounds__(KernelTraits<UMMA_N, SWAP>::THREADS, 1)
+fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
+                  const __grid_constant__ CUtensorMap tm_wgt, const KParams p) {
+  using T = KernelTraits<UMMA_N, SWAP>;
+  constexpr int NPW = T::NPW, CPT = T::CPT, CH = T::CH, NCH = T::NCH, TT = T::TT, WT = T::WT;
+  constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES, ROW_BYTES = T::ROW_BYTES;
+  constexpr uint32_t IDESC = ptx::idesc_f8_m128(UMMA_N);
+
+  extern __shared__ unsigned char smem_raw[];
+  // Operand tiles need 1024-byte alignment for the 128-byte swizzle.
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  unsigned char* smem = smem_raw + pad;
+  const uint32_t ring = raw_addr + pad;
+
+  const int kbn = p.kb_per_unit;
+  const int stages = p.stages;
+  float* tab_a = reinterpret_cast<float*>(smem + (size_t)stages * STAGE_BYTES);  // [2][kbn][TT]
+  float* tab_b = tab_a + 2 * kbn * TT;                                             // [2][kbn][2]
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tab_b + 2 * kbn * 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t bar_full = ptx::smem_u32(&ctl->full[0]);
+  const uint32_t bar_empty = ptx::smem_u32(&ctl->empty[0]);
+  const uint32_t bar_tfull = ptx::smem_u32(&ctl->tfull[0]);
+  const uint32_t bar_tempty = ptx::smem_u32(&ctl->tempty[0]);
+  const uint32_t bar_scfull = ptx::smem_u32(&ctl->scfull[0]);
+  const uint32_t bar_scempty = ptx::smem_u32(&ctl->scempty[0]);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(bar_full + 8 * s, 1);
+      ptx::mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(bar_tfull + 8 * b, 1);
+      ptx::mbar_init(bar_tempty + 8 * b, NPW);
+      ptx::mbar_init(bar_scfull + 8 * b, 64);
+      ptx::mbar_init(bar_scempty + 8 * b, NPW);
+    }
+    ctl->abort = 0;
+    ctl->last = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tm_tok);
+    ptx::prefetch_tensormap(&tm_wgt);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&ctl->tmem_base), T::TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  BoundedWait bw{&ctl->abort, p.status, p.timeout_ns};
+
+  // 384-thread variants: the four service warps hand registers to the eight promotion
+  // warps, which hold 128 accumulators plus two TMEM load buffers each.
+  if (warp < 4) {
+  if constexpr (NPW == 8) ptx::setmaxnreg_dec<64>();
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const CUtensorMap* row_map = SWAP ? &tm_wgt : &tm_tok;
+      const CUtensorMap* col_map = SWAP ? &tm_tok : &tm_wgt;
+      int stage = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
+        const UnitCoord c = decode_unit(u, p);
+        const int row_y = SWAP ? c.wi * 128 : c.ti * 128;
+        const int col_y = SWAP ? c.ti * UMMA_N : c.wi * UMMA_N;
+        const int kb0 = c.s * kbn;
+        for (int kb = 0; kb < kbn; ++kb) {
+          if (!bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
+          const uint32_t dst = ring + stage * STAGE_BYTES;
+          ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
+          ptx::tma_load_2d(dst, row_map, bar_full + 8 * stage, (kb0 + kb) * 128, row_y);
+          ptx::tma_load_2d(dst + ROW_BYTES, col_map, bar_full + 8 * stage, (kb0 + kb) * 128, col_y);
+          if (++stage == stages) { stage = 0; ph ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t ph = 0, it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
+        for (int kb = 0; kb < kbn; ++kb, ++it) {
+          const uint32_t buf = it & 1u, tph = (it >> 1) & 1u;
+          if (!bw.wait(bar_tempty + 8 * buf, tph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
+          if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t a_addr = ring + stage * STAGE_BYTES;
+          const uint64_t a_desc = ptx::smem_desc_k128(a_addr);
+          const uint64_t b_desc = ptx::smem_desc_k128(a_addr + ROW_BYTES);
+          const uint32_t d_tmem = tmem_base + buf * UMMA_N;
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k) {
+            // 32 fp8 = 32 bytes along K inside the swizzle span: +2 in 16-byte address units.
+            ptx::umma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, k);
+          }
+          ptx::umma_commit(bar_empty + 8 * stage);  // ring slot reusable once these MMAs retire
+          ptx::umma_commit(bar_tfull + 8 * buf);    // K-block partial ready for promotion
+          if (++stage == stages) { stage = 0; ph ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ scale loader
+    const int tid = threadIdx.x - 64;
+    uint32_t ui = 0;
+    for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
+      const UnitCoord c = decode_unit(u, p);
+      const uint32_t t = ui & 1u, tph = (ui >> 1) & 1u;
+      if (!bw.wait(bar_scempty + 8 * t, tph ^ 1u, kWaitLoaderEmpty)) break;
+      const int kb0 = c.s * kbn;
+      const int t0 = c.ti * TT;
+      float* ta = tab_a + t * kbn * TT;
+      float* tb = tab_b + t * kbn * 2;
+      const float* bs_row = p.Bs + (long long)(c.wi * (WT / 128)) * p.bs_sn;
+      const int total = kbn * TT;
+      if (p.as_sk == 1) {
+        // rows of As are contiguous: K-block index fastest across threads
+        for (int idx = tid; idx < total; idx += 64) {
+          const int x = idx / kbn, kb = idx - x * kbn;
+          const int tok = min(t0 + x, p.M - 1);
+          float v = __ldg(p.As + (long long)tok * p.as_sm + (kb0 + kb));
+          if (SWAP) v *= __ldg(bs_row + (long long)(kb0 + kb) * p.bs_sk);
+          ta[kb * TT + x] = v;
+        }
+      } else {
+        for (int idx = tid; idx < total; idx += 64) {
+          const int kb = idx / TT, x = idx - kb * TT;
+          const int tok = min(t0 + x, p.M - 1);
+          float v = __ldg(p.As + (long long)tok * p.as_sm + (long long)(kb0 + kb) * p.as_sk);
+          if (SWAP) v *= __ldg(bs_row + (long long)(kb0 + kb) * p.bs_sk);
+          ta[kb * TT + x] = v;
+        }
+      }
+      if (!SWAP) {
+        const int nblk_max = p.N / 128 - 1;
+        for (int idx = tid; idx < kbn * 2; idx += 64) {
+          const int kb = idx >> 1, h = idx & 1;
+          const int nb = min(c.wi * (WT / 128) + h, nblk_max);
+          tb[idx] = __ldg(p.Bs + (long long)nb * p.bs_sn + (long long)(kb0 + kb) * p.bs_sk);
+        }
+      }
+      ptx::mbar_arrive(bar_scfull + 8 * t);
+    }
+  }
+  } else {
+    // ------------------------------------------------- promotion + epilogue warps
+    if constexpr (NPW == 8) ptx::setmaxnreg_inc<216>();
+    const int pw = warp - 4;
+    const int q = warp & 3;      // TMEM lane quarter this warp may read
+    const int half = pw >> 2;    // which 128-column half of a 256-wide tile
+    const int row = q * 32 + lane;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * 128;
+    const bool leader = threadIdx.x == kProducerThreads;
+    uint32_t ui = 0, it = 0;
+    for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
+      const UnitCoord c = decode_unit(u, p);
+      const uint32_t t = ui & 1u, sph = (ui >> 1) & 1u;
+      bool ok = bw.wait(bar_scfull + 8 * t, sph, kWaitPromoScale);
+      const float* ta = tab_a + t * kbn * TT;
+      const float* tb = tab_b + t * kbn * 2;
+
+      float acc[CPT];
+#pragma unroll
+      for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
+
+      for (int kb = 0; kb < kbn && ok; ++kb, ++it) {
+        const uint32_t buf = it & 1u, tph = (it >> 1) & 1u;
+        float sc = 0.f;
+        if (!SWAP) sc = ta[kb * TT + row] * tb[kb * 2 + half];
+        const float4* sv = reinterpret_cast<const float4*>(ta + kb * TT + half * 128);
+        if (!bw.wait(bar_tfull + 8 * buf, tph, kWaitPromoTmemFull)) { ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t taddr = lane_base + buf * UMMA_N;
+        uint32_t d[2][CH];
+        ptx::tmem_ld<CH>(taddr, d[0]);
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch) {
+          ptx::tmem_wait_ld();
+          if (ch + 1 < NCH) ptx::tmem_ld<CH>(taddr + (ch + 1) * CH, d[(ch + 1) & 1]);
+          if (SWAP) {
+#pragma unroll
+            for (int i = 0; i < CH; i += 4) {
+              const float4 s4 = sv[(ch * CH + i) >> 2];
+              acc[ch * CH + i + 0] = fmaf(__uint_as_float(d[ch & 1][i + 0]), s4.x, acc[ch * CH + i + 0]);
+              acc[ch * CH + i + 1] = fmaf(__uint_as_float(d[ch & 1][i + 1]), s4.y, acc[ch * CH + i + 1]);
+              acc[ch * CH + i + 2] = fmaf(__uint_as_float(d[ch & 1][i + 2]), s4.z, acc[ch * CH + i + 2]);
+              acc[ch * CH + i + 3] = fmaf(__uint_as_float(d[ch & 1][i + 3]), s4.w, acc[ch * CH + i + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < CH; ++i)
+              acc[ch * CH + i] = fmaf(__uint_as_float(d[ch & 1][i]), sc, acc[ch * CH + i]);
+          }
+        }
+        // every lane's tcgen05.ld has completed (wait::ld above): hand the buffer back
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * buf);
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar_scempty + 8 * t);
+
+      // ------------------------------------------------------------- epilogue
+      if constexpr (SPLITK) {
+        // Split-K: park the fp32 partial; the CTA that arrives last on the tile's counter
+        // sums all partials in split order (bit-stable) and writes the tile.
+        const size_t tile_floats = (size_t)UMMA_N * 128;
+        float* part = p.ws_partial + ((size_t)c.tile * p.split + c.s) * tile_floats +
+                      (size_t)(half * 128) * 128 + row;
+        if (ok) {
+#pragma unroll
+          for (int j = 0; j < CPT; ++j) __stcg(part + j * 128, acc[j]);
+        }
+        __threadfence();
+        ptx::bar_sync(1, NPW * 32);
+        if (leader) {
+          int verdict = 2;  // 2 = a wait gave up somewhere in this CTA: stop
+          if (!ctl->abort) {
+            const int old = atomicAdd(p.ws_counter + c.tile, 1);
+            verdict = (old == p.split - 1) ? 1 : 0;
+          }
+          ctl->last = verdict;
+        }
+        ptx::bar_sync(1, NPW * 32);
+        const int verdict = ctl->last;
+        if (verdict == 2) break;
+        if (verdict == 0) continue;
+        __threadfence();
+        const float* base = p.ws_partial + (size_t)c.tile * p.split * tile_floats;
+        for (int s = 0; s < p.split; ++s) {
+          const float* src = base + s * tile_floats + (size_t)(half * 128) * 128 + row;
+#pragma unroll
+          for (int j0 = 0; j0 < CPT; j0 += 16) {
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __ldcg(src + (size_t)(j0 + i) * 128);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[j0 + i] = (s == 0) ? v[i] : acc[j0 + i] + v[i];
+            asm volatile("" ::: "memory");  // keep at most 16 loads in flight per thread
+          }
+        }
+        if (leader) atomicExch(p.ws_counter + c.tile, 0);
+      } else {
+        if (!ok) break;
+      }
+
+      if (SWAP) {
+        const int n = c.wi * 128 + row;
+        const int m_base = c.ti * TT + half * 128;
+        __nv_bfloat16* dst = p.C + (long long)m_base * p.ldc + n;
+        const int m_left = p.M - m_base;
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) {
+          if (j < m_left) *dst = __float2bfloat16_rn(acc[j]);
+          dst += p.ldc;
+        }
+      } else {
+        const int m = c.ti * 128 + row;
+        const int n = c.wi * WT + half * 128;
+        if (m < p.M && n < p.N) {
+          uint4* dst = reinterpret_cast<uint4*>(p.C + (long long)m * p.ldc + n);
+#pragma unroll
+          for (int j = 0; j < CPT; j += 8) {
+            __nv_bfloat162 v0 = __floats2bfloat162_rn(acc[j + 0], acc[j + 1]);
+            __nv_bfloat162 v1 = __floats2bfloat162_rn(acc[j + 2], acc[j + 3]);
+            __nv_bfloat162 v2 = __floats2bfloat162_rn(acc[j + 4], acc[j + 5]);
+            __nv_bfloat162 v3 = __floats2bfloat162_rn(acc[j + 6], acc[j + 7]);
+            uint4 o;
+            o.x = *reinterpret_cast<uint32_t*>(&v0);
+            o.y = *reinterpret_cast<uint32_t*>(&v1);
+            o.z = *reinterpret_cast<uint32_t*>(&v2);
+            o.w = *reinterpret_cast<uint32_t*>(&v3);
+            dst[j >> 3] = o;
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (ctl->abort) __nanosleep(1000000);  // let copies that are still in flight land
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
+}  // namespace fp8mm

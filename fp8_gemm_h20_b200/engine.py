@@ -1,0 +1,116 @@
+"""Kernel registry: table `impl` name -> launcher over the native sm_100a library.
+
+Same surface as the reference registry (fp8_gemm_h20/engine.py:5-19): `KERNELS`,
+`kernel(name)` returning `fn(A, B, As, Bs, config) -> C`, and `run(entry, args)`.
+The callables here do what the reference's per-kernel host wrappers did
+(kernels/kernel_v2.py:339-376): merge defaults, keep a zeroed workspace per
+(device, stream), allocate the bf16 output, and enqueue one launch on the current
+stream.  The kernels themselves are CUDA (csrc/fp8mm_kernel.cuh), not JIT code.
+"""
+import ctypes
+from functools import lru_cache
+
+from . import _lib
+
+# impl name -> (native impl id, defaults merged under the table's config)
+KERNELS = {
+    "umma": (_lib.IMPL_UMMA, {"BLOCK_T": 128, "BLOCK_W": 256, "NUM_STAGES": 4, "SPLIT": 1,
+                              "GROUP_SIZE_M": 8, "MAX_CTAS": 0}),
+    "umma_swap": (_lib.IMPL_UMMA_SWAP, {"BLOCK_T": 16, "BLOCK_W": 128, "NUM_STAGES": 8, "SPLIT": 1,
+                                        "GROUP_SIZE_M": 1, "MAX_CTAS": 0}),
+}
+
+_MIN_WORKSPACE = 1 << 20          # bytes; grown on demand, never shrunk
+_workspaces = {}                  # (device index, stream handle) -> uint8 tensor
+
+
+def make_cfg(impl, config):
+    """Table entry -> native fp8mm_cfg."""
+    impl_id, defaults = KERNELS[impl]
+    c = dict(defaults)
+    c.update(config)
+    return _lib.Cfg(impl=impl_id, block_t=int(c["BLOCK_T"]), block_w=int(c["BLOCK_W"]),
+                    stages=int(c["NUM_STAGES"]), split=int(c["SPLIT"]),
+                    group_m=int(c["GROUP_SIZE_M"]), max_ctas=int(c.get("MAX_CTAS", 0)), flags=0)
+
+
+def _workspace(torch, device, stream, nbytes):
+    """Zeroed scratch (status word, split-K counters, fp32 partials), one per (device, stream)
+    as in the reference (kernel_v2.py:309-324).  Never reallocated while capturing a graph."""
+    key = (device.index, stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("fp8mm workspace must exist before CUDA-graph capture: "
+                               "call matmul once on this stream with these shapes first")
+        size = max(_MIN_WORKSPACE, int(nbytes))
+        ws = torch.zeros(size, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def launch(A, B, As, Bs, impl, config, out=None):
+    """Enqueue C = blockscaled(A @ B^T) on the current stream of A.device and return C.
+
+    `out`, when given, is a bf16 [M, N] view whose rows may be strided (row stride a
+    multiple of 8 elements): the N-sharded layer writes shards into a wider buffer."""
+    import torch
+    lib = _lib.load()
+    m, k = A.shape
+    n = B.shape[0]
+    cfg = make_cfg(impl, config)
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=A.device)
+    elif out.dtype != torch.bfloat16 or tuple(out.shape) != (m, n) or out.stride(1) != 1:
+        raise ValueError("out must be a bfloat16 [M,N] tensor with unit column stride")
+    stream = torch.cuda.current_stream(A.device).cuda_stream
+    need = lib.fp8mm_b200_workspace_bytes(m, n, k, ctypes.byref(cfg))
+    if need == 0:
+        rc = lib.fp8mm_b200_validate(m, n, k, ctypes.byref(cfg))
+        raise ValueError(f"fp8mm: {_lib.strerror(rc)} (impl={impl}, config={dict(config)}, M,N,K={m},{n},{k})")
+    ws = _workspace(torch, A.device, stream, need)
+    args = _lib.Args(A=A.data_ptr(), B=B.data_ptr(), As=As.data_ptr(), Bs=Bs.data_ptr(), C=out.data_ptr(),
+                     M=m, N=n, K=k, reserved0=0,
+                     as_stride_m=As.stride(0), as_stride_k=As.stride(1),
+                     bs_stride_n=Bs.stride(0), bs_stride_k=Bs.stride(1), ldc=out.stride(0))
+    rc = lib.fp8mm_b200_gemm(ctypes.byref(args), ctypes.byref(cfg), ws.data_ptr(), ws.numel(), stream)
+    if rc != 0:
+        raise RuntimeError(f"fp8mm_b200_gemm failed: {_lib.strerror(rc)} "
+                           f"(impl={impl}, config={dict(config)}, M,N,K={m},{n},{k})")
+    return out
+
+
+def device_status(device=None):
+    """Synchronise and return (code, detail) of the workspaces on `device`: code 0 unless a
+    bounded device-side wait gave up (then the kernel left early and the output is invalid)."""
+    import torch
+    lib = _lib.load()
+    worst = (0, 0)
+    for (dev, _stream), ws in list(_workspaces.items()):
+        if device is not None and torch.device(device).index not in (None, dev):
+            continue
+        torch.cuda.synchronize(dev)
+        detail = ctypes.c_int32(0)
+        with torch.cuda.device(dev):
+            rc = lib.fp8mm_b200_last_status(ws.data_ptr(), ctypes.byref(detail))
+        if rc != 0:
+            worst = (rc, detail.value)
+    return worst
+
+
+@lru_cache(maxsize=None)
+def kernel(name):
+    """Callable `fn(A, B, As, Bs, config)` for a table `impl` name (engine.py:13-16)."""
+    if name not in KERNELS:
+        raise KeyError(name)
+
+    def fn(A, B, As, Bs, config):
+        return launch(A, B, As, Bs, name, config)
+
+    fn.__name__ = f"block_fp8_gemm_{name}_b200"
+    return fn
+
+
+def run(entry, args):
+    """Run a table entry on (A, B, As, Bs) (engine.py:18-19)."""
+    return kernel(entry["impl"])(*args, dict(entry["config"]))

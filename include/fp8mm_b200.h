@@ -1,0 +1,125 @@
+/*
+ * fp8mm_b200.h — C ABI of the B200 (sm_100a) block-scaled FP8 GEMM library.
+ *
+ *   C[M,N] (bf16) = sum_kb ( A_e4m3[M, 128kb..] . B_e4m3[N, 128kb..]^T ) * As[M,kb] * Bs[N/128,kb]
+ *
+ * This is the boundary a foreign-function binding attaches to.  It replaces the
+ * kernel registry and the per-kernel host wrappers of the reference project:
+ *   fp8_gemm_h20/engine.py:5-19            (name -> kernel, run(entry, args))
+ *   fp8_gemm_h20/kernels/kernel_v2.py:339-376   (config merge, split legalisation,
+ *                                           workspace, output allocation, launch)
+ *   fp8_gemm_h20/kernels/baseline_gluon.py:259-293, baseline_triton.py:87-114,
+ *   kernel_scale_tma.py:356-396, kernel_shortk.py:46-54   (the other wrappers)
+ *
+ * Plain pointers and sizes only: no torch types, no C++ types.  Every function
+ * returns 0 on success or a negative FP8MM_E_* code; nothing throws, traps or
+ * aborts.  All launches are asynchronous on the stream that is passed in.
+ */
+#ifndef FP8MM_B200_H_
+#define FP8MM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- error codes -------------------------------------------------------- */
+#define FP8MM_OK                0
+#define FP8MM_E_NULL           -1   /* a required pointer is NULL                      */
+#define FP8MM_E_SHAPE          -2   /* M<1, or N or K not a multiple of 128            */
+#define FP8MM_E_CONFIG         -3   /* tile / split / stage combination not legal      */
+#define FP8MM_E_WORKSPACE      -4   /* workspace missing or smaller than required      */
+#define FP8MM_E_ALIGN          -5   /* A or B not 16-byte aligned, C not 16-byte aligned */
+#define FP8MM_E_DRIVER         -6   /* tensor-map encode or another driver call failed */
+#define FP8MM_E_LAUNCH         -7   /* the kernel launch itself was refused            */
+#define FP8MM_E_DEVICE_TIMEOUT -8   /* a bounded device-side wait gave up (see status) */
+
+/* ---- kernel families ("impl" names of the JSON tuning tables) ------------ */
+#define FP8MM_IMPL_UMMA        0    /* tokens on the 128 UMMA rows, weights on UMMA-N (128|256)  */
+#define FP8MM_IMPL_UMMA_SWAP   1    /* swap-AB: weights on the 128 UMMA rows, tokens on UMMA-N   */
+
+/*
+ * Operands.  Strides are in ELEMENTS and are exactly the values the reference
+ * hands to its kernels (kernel_v2.py:371-372: As.stride(0), As.stride(1),
+ * Bs.stride(0), Bs.stride(1)); ldc is new so that an N-shard can write into a
+ * column slice of a wider C.
+ *   A  [M,K]      float8_e4m3fn, row-major, contiguous (ld = K)     dispatch.py:22
+ *   B  [N,K]      float8_e4m3fn, row-major, contiguous (ld = K)     dispatch.py:22
+ *   As [M,K/128]  float32, any strides                              dispatch.py:24-27
+ *   Bs [N/128,K/128] float32, any strides                           dispatch.py:24-27
+ *   C  [M,N]      bfloat16, row stride ldc >= N
+ */
+typedef struct fp8mm_args {
+  const void*  A;
+  const void*  B;
+  const float* As;
+  const float* Bs;
+  void*        C;
+  int32_t      M, N, K;
+  int32_t      reserved0;
+  int64_t      as_stride_m, as_stride_k;
+  int64_t      bs_stride_n, bs_stride_k;
+  int64_t      ldc;
+} fp8mm_args;
+
+/*
+ * Launch configuration = one "config" object of a tuning-table entry
+ * (fp8_gemm_h20/configs/*.json, "entries"/"N,K"/"M"/{"impl","config"}).
+ *   block_t   token tile   (BLOCK_T):  UMMA   -> 128;  UMMA_SWAP -> 16,32,64,128,256
+ *   block_w   weight tile  (BLOCK_W):  UMMA   -> 128 or 256;  UMMA_SWAP -> 128
+ *   stages    depth of the TMA shared-memory ring (NUM_STAGES); clipped to what fits
+ *   split     split-K factor (SPLIT); a value that does not divide K/128 is
+ *             legalised to 1, as the reference wrapper does (kernel_v2.py:355-356)
+ *   group_m   token tiles per raster group (GROUP_SIZE_M), >=1
+ *   max_ctas  0 = one wave sized from the SM count; otherwise an upper bound on the grid
+ */
+typedef struct fp8mm_cfg {
+  int32_t impl;
+  int32_t block_t;
+  int32_t block_w;
+  int32_t stages;
+  int32_t split;
+  int32_t group_m;
+  int32_t max_ctas;
+  int32_t flags;      /* reserved, must be 0 */
+} fp8mm_cfg;
+
+/* Legality of (M,N,K,cfg) without touching the GPU.  Replaces the per-wrapper
+ * asserts (kernel_v2.py:341-349, kernel_shortk.py:49) and the tile checks of
+ * config.py:44-56.  Returns FP8MM_OK or a negative code. */
+int fp8mm_b200_validate(int32_t M, int32_t N, int32_t K, const fp8mm_cfg* cfg);
+
+/* Bytes of zero-initialised device workspace the call needs (status words,
+ * split-K tile counters and fp32 partial tiles).  Replaces the per-(device,
+ * stream) workspace sizing of kernel_v2.py:309-324.  The same workspace must not
+ * be used by two launches that can overlap on the GPU: keep one per stream. */
+size_t fp8mm_b200_workspace_bytes(int32_t M, int32_t N, int32_t K, const fp8mm_cfg* cfg);
+
+/* Zero a fresh workspace on `stream` (a cudaStream_t).  Needed once after
+ * allocation; the kernels leave the counters at zero again after every launch
+ * (kernel_v2.py:289 does the same with atomic_xchg), so graph replay is safe. */
+int fp8mm_b200_workspace_init(void* workspace, size_t ws_bytes, void* stream);
+
+/* Enqueue one GEMM on `stream` (a cudaStream_t) of the current device.
+ * Replaces engine.run -> block_fp8_gemm_* (engine.py:18-19, kernel_v2.py:339-376).
+ * Inputs are borrowed until the enqueued work has run; nothing is allocated. */
+int fp8mm_b200_gemm(const fp8mm_args* args, const fp8mm_cfg* cfg,
+                    void* workspace, size_t ws_bytes, void* stream);
+
+/* After the stream has been synchronised: 0 if no bounded device-side wait gave
+ * up since the workspace was initialised, else FP8MM_E_DEVICE_TIMEOUT; *detail
+ * (optional) receives the role/barrier code recorded by the kernel.  Blocking. */
+int fp8mm_b200_last_status(const void* workspace, int32_t* detail);
+
+/* Text for an error code. */
+const char* fp8mm_b200_strerror(int code);
+
+/* Library/ABI version: major*1000 + minor. */
+int fp8mm_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FP8MM_B200_H_ */

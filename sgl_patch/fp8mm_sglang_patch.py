@@ -1,0 +1,108 @@
+"""Opt-in SGLang adapter: send SGLang's dense block-FP8 linear to fp8_gemm_h20.matmul.
+
+Same contract as the reference adapter (sgl_patch/fp8mm_sglang_patch.py:11-96): nothing
+happens unless FP8MM_ENABLE=1; then an import hook waits for
+`sglang.srt.layers.quantization.fp8_utils` and wraps its `dispatch_w8a8_block_fp8_linear`.
+Only when SGLang itself would have picked its DeepGEMM linear is the call redirected, and
+only for inputs the selected profile covers; everything else goes to SGLang's own function
+untouched, before any quantisation work.
+
+Environment:
+  FP8MM_ENABLE=1                   turn the adapter on
+  FP8MM_PROFILE=35b_tp1|122b_tp4   tuning profile (default 35b_tp1)
+  FP8MM_HOME=/path/to/this/repo    prepended to sys.path
+  FP8MM_DISABLE_DG_PRECOMPILE=1    also skip DeepGEMM's all-M JIT precompile, unused once patched
+"""
+import os
+import sys
+
+if os.environ.get("FP8MM_ENABLE") == "1":
+    sys.path.insert(0, os.environ.get("FP8MM_HOME", "/root/fp8mm"))
+    if os.environ.get("FP8MM_DISABLE_DG_PRECOMPILE") == "1":
+        os.environ["SGLANG_JIT_DEEPGEMM_PRECOMPILE"] = "0"
+
+    import importlib.abc
+    import importlib.machinery
+
+    _TARGET = "sglang.srt.layers.quantization.fp8_utils"
+
+    def _install(mod):
+        """Wrap mod.dispatch_w8a8_block_fp8_linear (reference :22-71)."""
+        import torch
+        import fp8_gemm_h20 as fp8mm
+        from fp8_gemm_h20.config import get_profile
+
+        profile = os.environ.get("FP8MM_PROFILE", "35b_tp1")
+        covered = sorted(get_profile(profile)["entries"])
+        sgl_dispatch = mod.dispatch_w8a8_block_fp8_linear
+        quantize = mod.sglang_per_token_group_quant_fp8
+        stats = {"ours": 0, "fallback": 0}
+
+        def eligible(input, weight, block_size, weight_scale, input_scale):
+            if input_scale is not None or input.dtype != torch.bfloat16:
+                return False
+            if weight_scale.dtype != torch.float32 or list(block_size) != [128, 128]:
+                return False
+            if getattr(mod, "DEEPGEMM_SCALE_UE8M0", False):
+                return False
+            if not (input.is_contiguous() and weight.is_contiguous()):
+                return False
+            if weight.dtype != torch.float8_e4m3fn:
+                return False
+            n, k = weight.shape
+            return fp8mm.supports(profile, input.numel() // k, n, k)
+
+        def wrap(sgl_linear):
+            def fp8mm_w8a8_block_fp8_linear(input, weight, block_size, weight_scale, input_scale=None, bias=None):
+                if not eligible(input, weight, block_size, weight_scale, input_scale):
+                    stats["fallback"] += 1
+                    return sgl_linear(input, weight, block_size, weight_scale, input_scale, bias)
+                stats["ours"] += 1
+                n, k = weight.shape
+                # row-major [M, K/128] float32 activation scales, the layout matmul expects
+                q, s = quantize(input.view(-1, k), block_size[1], column_major_scales=False,
+                                scale_tma_aligned=False)
+                out = fp8mm.matmul(q, weight, s, weight_scale, profile=profile)
+                if bias is not None:
+                    out = out + bias
+                return out.view(*input.shape[:-1], n)
+
+            fp8mm_w8a8_block_fp8_linear.fp8mm_stats = stats
+            return fp8mm_w8a8_block_fp8_linear
+
+        def patched_dispatch():
+            chosen = sgl_dispatch()
+            if chosen is not mod.deepgemm_w8a8_block_fp8_linear_with_fallback:
+                return chosen            # some other backend was selected: leave it alone
+            return wrap(chosen)
+
+        mod.dispatch_w8a8_block_fp8_linear = patched_dispatch
+        print(f"[fp8mm] patched {_TARGET}.dispatch_w8a8_block_fp8_linear "
+              f"(profile={profile}, table NK={covered}, "
+              f"dg_precompile={os.environ.get('SGLANG_JIT_DEEPGEMM_PRECOMPILE', '1')})",
+              file=sys.stderr, flush=True)
+
+    class _Loader(importlib.abc.Loader):
+        """Runs the real loader, then patches the freshly executed module."""
+
+        def __init__(self, inner):
+            self.inner = inner
+
+        def create_module(self, spec):
+            return self.inner.create_module(spec)
+
+        def exec_module(self, module):
+            self.inner.exec_module(module)
+            _install(module)
+
+    class _Finder(importlib.abc.MetaPathFinder):
+        def find_spec(self, name, path, target=None):
+            if name != _TARGET:
+                return None
+            spec = importlib.machinery.PathFinder.find_spec(name, path)
+            if spec is None or spec.loader is None:
+                return None
+            spec.loader = _Loader(spec.loader)
+            return spec
+
+    sys.meta_path.insert(0, _Finder())
