@@ -36,16 +36,18 @@ def make_cfg(impl, config):
 
 def _workspace(torch, device, stream, nbytes):
     """Zeroed scratch (status word, split-K counters, fp32 partials), one per (device, stream)
-    as in the reference (kernel_v2.py:309-324).  Never reallocated while capturing a graph."""
+    as in the reference (kernel_v2.py:309-324).  The cache is never touched while a CUDA graph
+    is being captured: a capture on a stream that has no workspace yet (torch.cuda.graph picks
+    its own side stream) gets a private zeroed buffer from the graph's memory pool instead,
+    at the price of one memset node per call; warm up on the capture stream to avoid it."""
     key = (device.index, stream)
     ws = _workspaces.get(key)
-    if ws is None or ws.numel() < nbytes:
-        if torch.cuda.is_current_stream_capturing():
-            raise RuntimeError("fp8mm workspace must exist before CUDA-graph capture: "
-                               "call matmul once on this stream with these shapes first")
-        size = max(_MIN_WORKSPACE, int(nbytes))
-        ws = torch.zeros(size, dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
+    if ws is not None and ws.numel() >= nbytes:
+        return ws
+    if torch.cuda.is_current_stream_capturing():
+        return torch.zeros(int(nbytes), dtype=torch.uint8, device=device)
+    ws = torch.zeros(max(_MIN_WORKSPACE, int(nbytes)), dtype=torch.uint8, device=device)
+    _workspaces[key] = ws
     return ws
 
 
