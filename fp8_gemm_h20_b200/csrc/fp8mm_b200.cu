@@ -17,11 +17,14 @@
 namespace fp8mm {
 namespace {
 
-constexpr size_t kStatusBytes = 256;         // status words at the head of the workspace
+// Workspace layout, identical for every call so that no call's fp32 partials can land where
+// another call expects its (zero) counters: [status 256 B][counters kMaxSplitTiles x 4 B][partials].
+constexpr size_t kStatusBytes = 256;
+constexpr int kMaxSplitTiles = 16384;
+constexpr size_t kCounterBytes = (size_t)kMaxSplitTiles * sizeof(int);
 constexpr size_t kMaxDynSmem = 232448;       // 227 KB opt-in dynamic shared memory per CTA
 constexpr int kMaxDevices = 64;
 
-size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct Geometry {
   int umma_n;       // UMMA N = columns of the accumulator tile
@@ -67,7 +70,8 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   g->tiles = g->t_tiles * g->w_tiles;
   g->kb_total = K / 128;
   // A split that does not divide the K-block count runs unsplit (kernel_v2.py:355-356).
-  g->split = (c->split > 1 && g->kb_total % c->split == 0) ? c->split : 1;
+  // So does a split over more tiles than the counter region holds (it could not pay off).
+  g->split = (c->split > 1 && g->kb_total % c->split == 0 && g->tiles <= kMaxSplitTiles) ? c->split : 1;
   g->kbn = g->kb_total / g->split;
   const int npw = g->umma_n == 256 ? 8 : 4;
   g->threads = kProducerThreads + npw * 32;
@@ -88,7 +92,7 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   const size_t floor_smem = tmem_cols * 456 - 1024;  // (smem + 1 KB reserved) / 228 KB >= cols / 512
   if (smem < floor_smem) smem = floor_smem;
   g->smem = smem;
-  g->counter_bytes = g->split > 1 ? align_up((size_t)g->tiles * sizeof(int), 256) : 0;
+  g->counter_bytes = g->split > 1 ? kCounterBytes : 0;
   g->partial_bytes = g->split > 1 ? (size_t)g->tiles * g->split * g->umma_n * 128 * sizeof(float) : 0;
   return FP8MM_OK;
 }
