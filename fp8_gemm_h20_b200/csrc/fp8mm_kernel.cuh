@@ -264,24 +264,33 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       float* ta = tab_a + t * kbn * TT;
       float* tb = tab_b + t * kbn * 2;
       const float* bs_row = p.Bs + (long long)(c.wi * (WT / 128)) * p.bs_sn;
+      // kbn*TT activation scales (times the tile's weight scale when SWAP), eight independent
+      // global loads in flight per thread.  Rows of a contiguous As are read K-block-fastest.
       const int total = kbn * TT;
-      if (p.as_sk == 1) {
-        // rows of As are contiguous: K-block index fastest across threads
-        for (int idx = tid; idx < total; idx += 64) {
-          const int x = idx / kbn, kb = idx - x * kbn;
-          const int tok = min(t0 + x, p.M - 1);
-          float v = __ldg(p.As + (long long)tok * p.as_sm + (kb0 + kb));
-          if (SWAP) v *= __ldg(bs_row + (long long)(kb0 + kb) * p.bs_sk);
-          ta[kb * TT + x] = v;
+      const bool k_fastest = p.as_sk == 1;
+      constexpr int U = 8;
+      for (int base = tid; base < total; base += 64 * U) {
+        float v[U], w[U];
+        int dst[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int idx = base + u * 64;
+          v[u] = 0.f;
+          w[u] = 1.f;
+          dst[u] = -1;
+          if (idx < total) {
+            int x, kb;
+            if (k_fastest) { x = idx / kbn; kb = idx - x * kbn; }
+            else { kb = idx / TT; x = idx - kb * TT; }
+            const int tok = min(t0 + x, p.M - 1);
+            v[u] = __ldg(p.As + (long long)tok * p.as_sm + (long long)(kb0 + kb) * p.as_sk);
+            if (SWAP) w[u] = __ldg(bs_row + (long long)(kb0 + kb) * p.bs_sk);
+            dst[u] = kb * TT + x;
+          }
         }
-      } else {
-        for (int idx = tid; idx < total; idx += 64) {
-          const int kb = idx / TT, x = idx - kb * TT;
-          const int tok = min(t0 + x, p.M - 1);
-          float v = __ldg(p.As + (long long)tok * p.as_sm + (long long)(kb0 + kb) * p.as_sk);
-          if (SWAP) v *= __ldg(bs_row + (long long)(kb0 + kb) * p.bs_sk);
-          ta[kb * TT + x] = v;
-        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (dst[u] >= 0) ta[dst[u]] = v[u] * w[u];
       }
       if (!SWAP) {
         const int nblk_max = p.N / 128 - 1;
