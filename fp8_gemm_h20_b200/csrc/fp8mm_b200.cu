@@ -77,7 +77,8 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   g->threads = kProducerThreads + npw * 32;
   const size_t stage_bytes = 128 * 128 + (size_t)g->umma_n * 128;
   const size_t tab_bytes = 2 * (size_t)g->kbn * g->tt * sizeof(float) + 2 * (size_t)g->kbn * 2 * sizeof(float);
-  const size_t fixed = 1024 + tab_bytes + sizeof(SharedCtl);
+  const size_t staging = g->swap ? 0 : (size_t)npw * 4096;   // bf16 output staging for TMA stores
+  const size_t fixed = 1024 + staging + tab_bytes + sizeof(SharedCtl);
   if (fixed + 2 * stage_bytes > kMaxDynSmem) return FP8MM_E_CONFIG;
   int stages = c->stages > 0 ? c->stages : 4;
   const int fit = (int)((kMaxDynSmem - fixed) / stage_bytes);
@@ -167,6 +168,21 @@ int get_tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* 
   return FP8MM_OK;
 }
 
+// bf16 C [M, N] with row stride ldc, box = 32 rows x 64 columns (128 bytes), 128-byte swizzle.
+// Not cached: the output pointer is new on almost every call.
+int make_output_map(void* c, int m, int n, long long ldc, CUtensorMap* out) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return FP8MM_E_DRIVER;
+  cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)m};
+  cuuint64_t strides[1] = {(cuuint64_t)ldc * 2};
+  cuuint32_t box[2] = {64u, 32u};
+  cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FP8MM_OK : FP8MM_E_DRIVER;
+}
+
 // ----------------------------------------------------------------- launch
 struct DeviceInfo {
   int sms = 0;
@@ -186,7 +202,7 @@ unsigned long long timeout_ns() {
 
 template <int UMMA_N, bool SWAP, bool SPLITK>
 int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
-           const KParams& p, int grid, cudaStream_t stream) {
+               const CUtensorMap& tm_out, const KParams& p, int grid, cudaStream_t stream) {
   auto kern = fp8mm_umma_kernel<UMMA_N, SWAP, SPLITK>;
   {
     std::lock_guard<std::mutex> lk(g_mu);
@@ -197,15 +213,16 @@ int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, 
       g_dev[dev].attr_set[slot] = true;
     }
   }
-  kern<<<grid, g.threads, g.smem, stream>>>(tm_tok, tm_wgt, p);
+  kern<<<grid, g.threads, g.smem, stream>>>(tm_tok, tm_wgt, tm_out, p);
   return cudaGetLastError() == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
 }
 
 template <int UMMA_N, bool SWAP>
 int launch(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
-           const KParams& p, int grid, cudaStream_t stream) {
-  if (g.split > 1) return launch_one<UMMA_N, SWAP, true>(2 * slot + 1, dev, g, tm_tok, tm_wgt, p, grid, stream);
-  return launch_one<UMMA_N, SWAP, false>(2 * slot, dev, g, tm_tok, tm_wgt, p, grid, stream);
+           const CUtensorMap& tm_out, const KParams& p, int grid, cudaStream_t stream) {
+  if (g.split > 1)
+    return launch_one<UMMA_N, SWAP, true>(2 * slot + 1, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
+  return launch_one<UMMA_N, SWAP, false>(2 * slot, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
 }
 
 }  // namespace
@@ -288,6 +305,14 @@ int fp8mm_b200_gemm(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace, 
   rc = get_tensor_map(a->B, a->N, a->K, g.swap ? 128 : g.umma_n, &tm_wgt);
   if (rc != FP8MM_OK) return rc;
 
+  CUtensorMap tm_out;
+  if (g.swap) {
+    memset(&tm_out, 0, sizeof(tm_out));
+  } else {
+    rc = make_output_map(a->C, a->M, a->N, a->ldc, &tm_out);
+    if (rc != FP8MM_OK) return rc;
+  }
+
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   KParams p;
   p.As = a->As;
@@ -324,16 +349,16 @@ int fp8mm_b200_gemm(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace, 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (g.swap) {
     switch (g.umma_n) {
-      case 16: return launch<16, true>(0, dev, g, tm_tok, tm_wgt, p, grid, stream);
-      case 32: return launch<32, true>(1, dev, g, tm_tok, tm_wgt, p, grid, stream);
-      case 64: return launch<64, true>(2, dev, g, tm_tok, tm_wgt, p, grid, stream);
-      case 128: return launch<128, true>(3, dev, g, tm_tok, tm_wgt, p, grid, stream);
-      case 256: return launch<256, true>(4, dev, g, tm_tok, tm_wgt, p, grid, stream);
+      case 16: return launch<16, true>(0, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
+      case 32: return launch<32, true>(1, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
+      case 64: return launch<64, true>(2, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
+      case 128: return launch<128, true>(3, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
+      case 256: return launch<256, true>(4, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
     }
   } else {
     switch (g.umma_n) {
-      case 128: return launch<128, false>(5, dev, g, tm_tok, tm_wgt, p, grid, stream);
-      case 256: return launch<256, false>(6, dev, g, tm_tok, tm_wgt, p, grid, stream);
+      case 128: return launch<128, false>(5, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
+      case 256: return launch<256, false>(6, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
     }
   }
   return FP8MM_E_CONFIG;

@@ -132,13 +132,16 @@ struct KernelTraits {
   static constexpr uint32_t COL_BYTES = UMMA_N * 128u;
   static constexpr uint32_t STAGE_BYTES = ROW_BYTES + COL_BYTES;
   static constexpr uint32_t TMEM_COLS = 2 * UMMA_N < 32 ? 32 : 2 * UMMA_N;
+  // bf16 output staging for TMA stores (token-major tiles): 32 rows x 64 columns per warp
+  static constexpr uint32_t STAGING_BYTES = SWAP ? 0u : NPW * 4096u;
   static_assert(SWAP || UMMA_N >= 128, "token-major tiles carry 128 or 256 weight rows");
 };
 
 template <int UMMA_N, bool SWAP, bool SPLITK>
 __global__ void __launch_bounds__(KernelTraits<UMMA_N, SWAP>::THREADS, 1)
 fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
-                  const __grid_constant__ CUtensorMap tm_wgt, const KParams p) {
+                  const __grid_constant__ CUtensorMap tm_wgt,
+                  const __grid_constant__ CUtensorMap tm_out, const KParams p) {
   using T = KernelTraits<UMMA_N, SWAP>;
   constexpr int NPW = T::NPW, CPT = T::CPT, CH = T::CH, NCH = T::NCH, TT = T::TT, WT = T::WT;
   constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES, ROW_BYTES = T::ROW_BYTES;
@@ -153,7 +156,9 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
 
   const int kbn = p.kb_per_unit;
   const int stages = p.stages;
-  float* tab_a = reinterpret_cast<float*>(smem + (size_t)stages * STAGE_BYTES);  // [2][kbn][TT]
+  const uint32_t staging = ring + stages * STAGE_BYTES;   // 1024-byte aligned, NPW x 4 KB
+  unsigned char* staging_ptr = smem + (size_t)stages * STAGE_BYTES;
+  float* tab_a = reinterpret_cast<float*>(staging_ptr + T::STAGING_BYTES);       // [2][kbn][TT]
   float* tab_b = tab_a + 2 * kbn * TT;                                             // [2][kbn][2]
   SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tab_b + 2 * kbn * 2);
 
@@ -183,6 +188,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tm_tok);
     ptx::prefetch_tensormap(&tm_wgt);
+    if (!SWAP) ptx::prefetch_tensormap(&tm_out);
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(&ctl->tmem_base), T::TMEM_COLS);
@@ -264,33 +270,34 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       float* ta = tab_a + t * kbn * TT;
       float* tb = tab_b + t * kbn * 2;
       const float* bs_row = p.Bs + (long long)(c.wi * (WT / 128)) * p.bs_sn;
-      // kbn*TT activation scales (times the tile's weight scale when SWAP), eight independent
-      // global loads in flight per thread.  Rows of a contiguous As are read K-block-fastest.
-      const int total = kbn * TT;
-      const bool k_fastest = p.as_sk == 1;
+      // kbn*TT activation scales (times the tile's weight scale when SWAP).  A thread owns one
+      // token (column x of the table) and a stride of K blocks; no divisions, up to eight
+      // independent global loads in flight, conflict-free shared-memory stores.
+      constexpr int TPT = TT >= 64 ? 64 : TT;   // loader threads along the token axis
+      constexpr int KP = 64 / TPT;              // loader threads along the K-block axis
       constexpr int U = 8;
-      for (int base = tid; base < total; base += 64 * U) {
-        float v[U], w[U];
-        int dst[U];
+      const int x0 = tid % TPT, kp = tid / TPT;
+      for (int x = x0; x < TT; x += TPT) {
+        const int tok = min(t0 + x, p.M - 1);
+        const float* src = p.As + (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
+        const float* bsrc = bs_row + (long long)kb0 * p.bs_sk;
+        for (int kb = kp; kb < kbn; kb += KP * U) {
+          float v[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int idx = base + u * 64;
-          v[u] = 0.f;
-          w[u] = 1.f;
-          dst[u] = -1;
-          if (idx < total) {
-            int x, kb;
-            if (k_fastest) { x = idx / kbn; kb = idx - x * kbn; }
-            else { kb = idx / TT; x = idx - kb * TT; }
-            const int tok = min(t0 + x, p.M - 1);
-            v[u] = __ldg(p.As + (long long)tok * p.as_sm + (long long)(kb0 + kb) * p.as_sk);
-            if (SWAP) w[u] = __ldg(bs_row + (long long)(kb0 + kb) * p.bs_sk);
-            dst[u] = kb * TT + x;
+          for (int u = 0; u < U; ++u) {
+            const int kbu = kb + u * KP;
+            v[u] = 0.f;
+            if (kbu < kbn) {
+              v[u] = __ldg(src + (long long)kbu * p.as_sk);
+              if (SWAP) v[u] *= __ldg(bsrc + (long long)kbu * p.bs_sk);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int kbu = kb + u * KP;
+            if (kbu < kbn) ta[kbu * TT + x] = v[u];
           }
         }
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (dst[u] >= 0) ta[dst[u]] = v[u] * w[u];
       }
       if (!SWAP) {
         const int nblk_max = p.N / 128 - 1;
@@ -416,26 +423,44 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           dst += p.ldc;
         }
       } else {
-        const int m = c.ti * 128 + row;
-        const int n = c.wi * WT + half * 128;
-        if (m < p.M && n < p.N) {
-          uint4* dst = reinterpret_cast<uint4*>(p.C + (long long)m * p.ldc + n);
+        // Coalesced bf16 epilogue: each warp stages its 32 rows x 64 columns in shared memory
+        // (128-byte rows, 16-byte chunks XOR-swizzled by row so the writes are conflict-free)
+        // and one lane hands the slab to the TMA unit, which clips it at the edges of C.
+        const int m0w = c.ti * 128 + q * 32;
+        const int n0 = c.wi * WT + half * 128;
+        if (m0w < p.M && n0 < p.N) {
+          unsigned char* stg = staging_ptr + pw * 4096;
+          const uint32_t stg_addr = staging + pw * 4096;
 #pragma unroll
-          for (int j = 0; j < CPT; j += 8) {
-            __nv_bfloat162 v0 = __floats2bfloat162_rn(acc[j + 0], acc[j + 1]);
-            __nv_bfloat162 v1 = __floats2bfloat162_rn(acc[j + 2], acc[j + 3]);
-            __nv_bfloat162 v2 = __floats2bfloat162_rn(acc[j + 4], acc[j + 5]);
-            __nv_bfloat162 v3 = __floats2bfloat162_rn(acc[j + 6], acc[j + 7]);
-            uint4 o;
-            o.x = *reinterpret_cast<uint32_t*>(&v0);
-            o.y = *reinterpret_cast<uint32_t*>(&v1);
-            o.z = *reinterpret_cast<uint32_t*>(&v2);
-            o.w = *reinterpret_cast<uint32_t*>(&v3);
-            dst[j >> 3] = o;
+          for (int sl = 0; sl < CPT / 64; ++sl) {
+            if (lane == 0) ptx::bulk_wait_read_all();   // the previous slab has left the staging buffer
+            __syncwarp();
+#pragma unroll
+            for (int ck = 0; ck < 8; ++ck) {
+              const int j = sl * 64 + ck * 8;
+              __nv_bfloat162 v0 = __floats2bfloat162_rn(acc[j + 0], acc[j + 1]);
+              __nv_bfloat162 v1 = __floats2bfloat162_rn(acc[j + 2], acc[j + 3]);
+              __nv_bfloat162 v2 = __floats2bfloat162_rn(acc[j + 4], acc[j + 5]);
+              __nv_bfloat162 v3 = __floats2bfloat162_rn(acc[j + 6], acc[j + 7]);
+              uint4 o;
+              o.x = *reinterpret_cast<uint32_t*>(&v0);
+              o.y = *reinterpret_cast<uint32_t*>(&v1);
+              o.z = *reinterpret_cast<uint32_t*>(&v2);
+              o.w = *reinterpret_cast<uint32_t*>(&v3);
+              *reinterpret_cast<uint4*>(stg + lane * 128 + ((ck ^ (lane & 7)) << 4)) = o;
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_2d(&tm_out, stg_addr, n0 + sl * 64, m0w);
+              ptx::bulk_commit_group();
+            }
           }
         }
       }
     }
+    if (!SWAP && lane == 0) ptx::bulk_wait_read_all();
+    __syncwarp();
   }
 
   // ---------------------------------------------------------------- teardown
