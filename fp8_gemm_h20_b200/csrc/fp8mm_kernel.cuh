@@ -50,8 +50,8 @@ struct KParams {
 struct __align__(8) SharedCtl {
   unsigned long long full[kMaxStages];
   unsigned long long empty[kMaxStages];
-  unsigned long long tfull[2];
-  unsigned long long tempty[2];
+  unsigned long long tfull[4];    // [TMEM buffer][column half]
+  unsigned long long tempty[4];
   unsigned long long scfull[2];
   unsigned long long scempty[2];
   unsigned int tmem_base;
@@ -132,6 +132,11 @@ struct KernelTraits {
   static constexpr uint32_t COL_BYTES = UMMA_N * 128u;
   static constexpr uint32_t STAGE_BYTES = ROW_BYTES + COL_BYTES;
   static constexpr uint32_t TMEM_COLS = 2 * UMMA_N < 32 ? 32 : 2 * UMMA_N;
+  // A 256-column K-block partial is produced and consumed as two independent 128-column
+  // halves (own MMAs, own full/empty barriers, own promotion warps): four short
+  // MMA -> promote -> release chains in flight instead of two long ones.
+  static constexpr int HALVES = UMMA_N == 256 ? 2 : 1;
+  static constexpr int NH = UMMA_N / HALVES;                  // N of one tcgen05.mma
   // bf16 output staging for TMA stores (token-major tiles): 32 rows x 64 columns per warp
   static constexpr uint32_t STAGING_BYTES = SWAP ? 0u : NPW * 4096u;
   static_assert(SWAP || UMMA_N >= 128, "token-major tiles carry 128 or 256 weight rows");
@@ -145,7 +150,8 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   using T = KernelTraits<UMMA_N, SWAP>;
   constexpr int NPW = T::NPW, CPT = T::CPT, CH = T::CH, NCH = T::NCH, TT = T::TT, WT = T::WT;
   constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES, ROW_BYTES = T::ROW_BYTES;
-  constexpr uint32_t IDESC = ptx::idesc_f8_m128(UMMA_N);
+  constexpr int HALVES = T::HALVES, NH = T::NH;
+  constexpr uint32_t IDESC = ptx::idesc_f8_m128(NH);
 
   extern __shared__ unsigned char smem_raw[];
   // Operand tiles need 1024-byte alignment for the 128-byte swizzle.
@@ -177,9 +183,11 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       ptx::mbar_init(bar_full + 8 * s, 1);
       ptx::mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < 4; ++b) {
       ptx::mbar_init(bar_tfull + 8 * b, 1);
-      ptx::mbar_init(bar_tempty + 8 * b, NPW);
+      ptx::mbar_init(bar_tempty + 8 * b, NPW / HALVES);
+    }
+    for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(bar_scfull + 8 * b, 64);
       ptx::mbar_init(bar_scempty + 8 * b, NPW);
     }
@@ -238,20 +246,25 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
         for (int kb = 0; kb < kbn; ++kb, ++it) {
           const uint32_t buf = it & 1u, tph = (it >> 1) & 1u;
-          if (!bw.wait(bar_tempty + 8 * buf, tph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
           if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
-          ptx::tc_fence_after();
           const uint32_t a_addr = ring + stage * STAGE_BYTES;
           const uint64_t a_desc = ptx::smem_desc_k128(a_addr);
-          const uint64_t b_desc = ptx::smem_desc_k128(a_addr + ROW_BYTES);
-          const uint32_t d_tmem = tmem_base + buf * UMMA_N;
 #pragma unroll
-          for (uint32_t k = 0; k < 4; ++k) {
-            // 32 fp8 = 32 bytes along K inside the swizzle span: +2 in 16-byte address units.
-            ptx::umma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, k);
+          for (uint32_t h = 0; h < (uint32_t)HALVES; ++h) {
+            const uint32_t tb_idx = buf * 2 + h;
+            if (!bw.wait(bar_tempty + 8 * tb_idx, tph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const uint64_t b_desc = ptx::smem_desc_k128(a_addr + ROW_BYTES + h * NH * 128);
+            const uint32_t d_tmem = tmem_base + buf * UMMA_N + h * NH;
+#pragma unroll
+            for (uint32_t k = 0; k < 4; ++k) {
+              // 32 fp8 = 32 bytes along K inside the swizzle span: +2 in 16-byte address units.
+              ptx::umma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, k);
+            }
+            ptx::umma_commit(bar_tfull + 8 * tb_idx);  // this half's K-block partial is ready
           }
-          ptx::umma_commit(bar_empty + 8 * stage);  // ring slot reusable once these MMAs retire
-          ptx::umma_commit(bar_tfull + 8 * buf);    // K-block partial ready for promotion
+          if (!ok) break;
+          ptx::umma_commit(bar_empty + 8 * stage);     // ring slot reusable once these MMAs retire
           if (++stage == stages) { stage = 0; ph ^= 1u; }
         }
       }
@@ -336,7 +349,8 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         float sc = 0.f;
         if (!SWAP) sc = ta[kb * TT + row] * tb[kb * 2 + half];
         const float4* sv = reinterpret_cast<const float4*>(ta + kb * TT + half * 128);
-        if (!bw.wait(bar_tfull + 8 * buf, tph, kWaitPromoTmemFull)) { ok = false; break; }
+        const uint32_t tb_idx = buf * 2 + (HALVES == 2 ? half : 0);
+        if (!bw.wait(bar_tfull + 8 * tb_idx, tph, kWaitPromoTmemFull)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t taddr = lane_base + buf * UMMA_N;
         uint32_t d[2][CH];
@@ -344,7 +358,15 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
 #pragma unroll
         for (int ch = 0; ch < NCH; ++ch) {
           ptx::tmem_wait_ld();
-          if (ch + 1 < NCH) ptx::tmem_ld<CH>(taddr + (ch + 1) * CH, d[(ch + 1) & 1]);
+          if (ch + 1 < NCH) {
+            ptx::tmem_ld<CH>(taddr + (ch + 1) * CH, d[(ch + 1) & 1]);
+          } else {
+            // every tcgen05.ld of this warp has completed: hand the buffer back before the
+            // last FMAs so the next MMA into it can be issued as early as possible
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * tb_idx);
+          }
           if (SWAP) {
 #pragma unroll
             for (int i = 0; i < CH; i += 4) {
@@ -360,10 +382,6 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
               acc[ch * CH + i] = fmaf(__uint_as_float(d[ch & 1][i]), sc, acc[ch * CH + i]);
           }
         }
-        // every lane's tcgen05.ld has completed (wait::ld above): hand the buffer back
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * buf);
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_scempty + 8 * t);
