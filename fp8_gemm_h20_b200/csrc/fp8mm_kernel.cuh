@@ -132,10 +132,10 @@ struct KernelTraits {
   static constexpr uint32_t COL_BYTES = UMMA_N * 128u;
   static constexpr uint32_t STAGE_BYTES = ROW_BYTES + COL_BYTES;
   static constexpr uint32_t TMEM_COLS = 2 * UMMA_N < 32 ? 32 : 2 * UMMA_N;
-  // A 256-column K-block partial is produced and consumed as two independent 128-column
-  // halves (own MMAs, own full/empty barriers, own promotion warps): four short
-  // MMA -> promote -> release chains in flight instead of two long ones.
-  static constexpr int HALVES = UMMA_N == 256 ? 2 : 1;
+  // A K-block partial can be produced and consumed as independent column halves (own MMAs,
+  // own barriers).  Measured slower: every tcgen05.commit costs the issuing thread ~250
+  // cycles, and halves double the commits.  Kept at 1.
+  static constexpr int HALVES = 1;
   static constexpr int NH = UMMA_N / HALVES;                  // N of one tcgen05.mma
   // bf16 output staging for TMA stores (token-major tiles): 32 rows x 64 columns per warp
   static constexpr uint32_t STAGING_BYTES = SWAP ? 0u : NPW * 4096u;
@@ -264,7 +264,8 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
             ptx::umma_commit(bar_tfull + 8 * tb_idx);  // this half's K-block partial is ready
           }
           if (!ok) break;
-          ptx::umma_commit(bar_empty + 8 * stage);     // ring slot reusable once these MMAs retire
+          // No second commit for the ring slot: a tcgen05.commit costs this thread ~250 cycles.
+          // The promotion warps see the same completion (tfull) and release the slot.
           if (++stage == stages) { stage = 0; ph ^= 1u; }
         }
       }
@@ -333,6 +334,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * 128;
     const bool leader = threadIdx.x == kProducerThreads;
     uint32_t ui = 0, it = 0;
+    int pstage = 0;              // ring slot of the K block being promoted
     for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
       const UnitCoord c = decode_unit(u, p);
       const uint32_t t = ui & 1u, sph = (ui >> 1) & 1u;
@@ -351,6 +353,9 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         const float4* sv = reinterpret_cast<const float4*>(ta + kb * TT + half * 128);
         const uint32_t tb_idx = buf * 2 + (HALVES == 2 ? half : 0);
         if (!bw.wait(bar_tfull + 8 * tb_idx, tph, kWaitPromoTmemFull)) { ok = false; break; }
+        // the MMAs of this K block have retired, so its operand tiles may be overwritten
+        if (leader) ptx::mbar_arrive(bar_empty + 8 * pstage);
+        if (++pstage == stages) pstage = 0;
         ptx::tc_fence_after();
         const uint32_t taddr = lane_base + buf * UMMA_N;
         uint32_t d[2][CH];
