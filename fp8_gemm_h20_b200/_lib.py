@@ -17,6 +17,7 @@ LIB_PATH = _PKG / LIB_NAME
 IMPL_UMMA = 0
 IMPL_UMMA_SWAP = 1
 E_DEVICE_TIMEOUT = -8
+E_TOO_LARGE = -9
 
 # every symbol include/fp8mm_b200.h declares
 SYMBOLS = (
@@ -24,6 +25,8 @@ SYMBOLS = (
     "fp8mm_b200_workspace_bytes",
     "fp8mm_b200_workspace_init",
     "fp8mm_b200_gemm",
+    "fp8mm_b200_gemm_static_scratch",
+    "fp8mm_b200_static_scratch_bytes",
     "fp8mm_b200_last_status",
     "fp8mm_b200_strerror",
     "fp8mm_b200_version",
@@ -81,6 +84,10 @@ def load():
         lib.fp8mm_b200_gemm.argtypes = [ctypes.POINTER(Args), ctypes.POINTER(Cfg), ctypes.c_void_p,
                                         ctypes.c_size_t, ctypes.c_void_p]
         lib.fp8mm_b200_gemm.restype = ctypes.c_int
+        lib.fp8mm_b200_gemm_static_scratch.argtypes = [ctypes.POINTER(Args), ctypes.POINTER(Cfg), ctypes.c_void_p]
+        lib.fp8mm_b200_gemm_static_scratch.restype = ctypes.c_int
+        lib.fp8mm_b200_static_scratch_bytes.argtypes = []
+        lib.fp8mm_b200_static_scratch_bytes.restype = ctypes.c_size_t
         lib.fp8mm_b200_last_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         lib.fp8mm_b200_last_status.restype = ctypes.c_int
         lib.fp8mm_b200_strerror.argtypes = [ctypes.c_int]

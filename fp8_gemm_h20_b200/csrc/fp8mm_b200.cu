@@ -228,6 +228,17 @@ int launch(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, cons
 }  // namespace
 }  // namespace fp8mm
 
+// ----------------------------------------------------- allocation-free entry point
+// Scratch for callers that cannot allocate: status word, split-K tile counters and fp32 partial
+// tiles in a buffer that is part of the library image.  Zero at load; counters are re-zeroed by
+// every call.  In host code `g_static_scratch` is only a handle for cudaGetSymbolAddress — the
+// device address it yields is what the kernels receive.
+constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+static void* g_static_scratch_addr[fp8mm::kMaxDevices] = {};  // per device, filled on first use
+
+
 using namespace fp8mm;
 
 extern "C" {
@@ -245,6 +256,8 @@ const char* fp8mm_b200_strerror(int code) {
     case FP8MM_E_DRIVER: return "CUDA driver call failed (tensor map encode)";
     case FP8MM_E_LAUNCH: return "kernel launch failed";
     case FP8MM_E_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case FP8MM_E_TOO_LARGE:
+      return "problem needs more scratch than the 8 MiB built into the allocation-free entry point";
     default: return "unknown error";
   }
 }
@@ -362,6 +375,33 @@ int fp8mm_b200_gemm(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace, 
     }
   }
   return FP8MM_E_CONFIG;
+}
+
+// ----------------------------------------------------- allocation-free entry point
+size_t fp8mm_b200_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int fp8mm_b200_gemm_static_scratch(const fp8mm_args* args, const fp8mm_cfg* cfg, void* stream) {
+  if (args == nullptr || cfg == nullptr) return FP8MM_E_NULL;
+  const size_t need = fp8mm_b200_workspace_bytes(args->M, args->N, args->K, cfg);
+  if (need == 0) return fp8mm_b200_validate(args->M, args->N, args->K, cfg);
+  if (need > kStaticScratchBytes) return FP8MM_E_TOO_LARGE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= fp8mm::kMaxDevices) return FP8MM_E_DRIVER;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(fp8mm::g_mu);
+    if (g_static_scratch_addr[dev] == nullptr) {
+      // once per device, with that device current: symbol -> device address
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return FP8MM_E_DRIVER;
+      g_static_scratch_addr[dev] = p;
+    }
+    scratch = g_static_scratch_addr[dev];
+  }
+  // status word + tile counters must start at zero whatever the previous call left behind
+  const size_t head = need < (size_t)(256 + 65536) ? need : (size_t)(256 + 65536);
+  if (cudaMemsetAsync(scratch, 0, head, static_cast<cudaStream_t>(stream)) != cudaSuccess) return FP8MM_E_DRIVER;
+  return fp8mm_b200_gemm(args, cfg, scratch, kStaticScratchBytes, stream);
 }
 
 }  // extern "C"

@@ -35,6 +35,8 @@ extern "C" {
 #define FP8MM_E_DRIVER         -6   /* tensor-map encode or another driver call failed */
 #define FP8MM_E_LAUNCH         -7   /* the kernel launch itself was refused            */
 #define FP8MM_E_DEVICE_TIMEOUT -8   /* a bounded device-side wait gave up (see status) */
+#define FP8MM_E_TOO_LARGE      -9   /* needs more scratch than the built-in buffer of the
+                                       allocation-free entry point holds                   */
 
 /* ---- kernel families ("impl" names of the JSON tuning tables) ------------ */
 #define FP8MM_IMPL_UMMA        0    /* tokens on the 128 UMMA rows, weights on UMMA-N (128|256)  */
@@ -107,6 +109,39 @@ int fp8mm_b200_workspace_init(void* workspace, size_t ws_bytes, void* stream);
  * Inputs are borrowed until the enqueued work has run; nothing is allocated. */
 int fp8mm_b200_gemm(const fp8mm_args* args, const fp8mm_cfg* cfg,
                     void* workspace, size_t ws_bytes, void* stream);
+
+/*
+ * Allocation-free variant of fp8mm_b200_gemm.  No counterpart in the reference: its wrappers
+ * allocate their split-K workspace with torch (kernel_v2.py:316-324) and so does the binding
+ * that ships with this library.
+ *
+ * Who needs it: hosts that must not (or cannot) call cudaMalloc on the GEMM path — an inference
+ * server that has handed every byte of device memory to its own pool allocator at start-up, a
+ * plug-in running inside someone else's memory-managed runtime, a real-time loop where an
+ * allocation would take the driver's global lock.  They still pass A, B, As, Bs and C; what
+ * they no longer have to provide is the scratch (status word, split-K tile counters, fp32
+ * partial tiles).  That scratch lives in a buffer compiled into the library, of
+ * fp8mm_b200_static_scratch_bytes() bytes (8 MiB), which every GPU that loads the library
+ * holds until the process exits.
+ *
+ *   - A (M, N, K, cfg) whose fp8mm_b200_workspace_bytes() exceeds that size is refused with
+ *     FP8MM_E_TOO_LARGE before anything is enqueued.  Every unsplit configuration fits.
+ *   - The first call on a device looks up the buffer's device address (a synchronous,
+ *     non-allocating runtime query, done with that device current).  Make that first call
+ *     before starting any stream capture on the device.
+ *   - The buffer is shared by all calls and keeps what the last call left in it.  Each call
+ *     re-zeroes the status word and the tile counters on `stream` before its kernel; the
+ *     partial tiles are always written before they are read.
+ *   - Because it is one shared buffer, two calls that can overlap on the GPU (different
+ *     streams, or different host threads on different streams) race on it.  Serialise them on
+ *     one stream, or use fp8mm_b200_gemm with one workspace per stream.
+ *   - Nothing here calls cudaMalloc, cudaFree or any allocating library routine.
+ * Results are the same bits fp8mm_b200_gemm produces for the same arguments.
+ */
+int fp8mm_b200_gemm_static_scratch(const fp8mm_args* args, const fp8mm_cfg* cfg, void* stream);
+
+/* Size in bytes of the built-in scratch buffer used by fp8mm_b200_gemm_static_scratch. */
+size_t fp8mm_b200_static_scratch_bytes(void);
 
 /* After the stream has been synchronised: 0 if no bounded device-side wait gave
  * up since the workspace was initialised, else FP8MM_E_DEVICE_TIMEOUT; *detail
