@@ -89,7 +89,8 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   size_t smem = fixed + stages * stage_bytes;
   // Shared memory share >= TMEM share, so that CTAs that fit on an SM together (this
   // kernel's or another stream's) can never ask for more than the 512 TMEM columns.
-  const size_t tmem_cols = 2 * g->umma_n < 32 ? 32 : 2 * g->umma_n;
+  const int nbuf = g->umma_n >= 128 ? 2 : (g->umma_n == 64 ? 4 : 8);   // KernelTraits::NBUF
+  const size_t tmem_cols = nbuf * g->umma_n < 32 ? 32 : (size_t)nbuf * g->umma_n;
   const size_t floor_smem = tmem_cols * 456 - 1024;  // (smem + 1 KB reserved) / 228 KB >= cols / 512
   if (smem < floor_smem) smem = floor_smem;
   g->smem = smem;
@@ -200,6 +201,16 @@ unsigned long long timeout_ns() {
   return v;
 }
 
+// Programmatic dependent launch lets a kernel's prologue overlap the previous kernel's tail;
+// FP8MM_PDL=0 turns it off.
+bool use_pdl() {
+  static const bool v = []() {
+    const char* e = getenv("FP8MM_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return v;
+}
+
 template <int UMMA_N, bool SWAP, bool SPLITK>
 int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
                const CUtensorMap& tm_out, const KParams& p, int grid, cudaStream_t stream) {
@@ -213,8 +224,19 @@ int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, 
       g_dev[dev].attr_set[slot] = true;
     }
   }
-  kern<<<grid, g.threads, g.smem, stream>>>(tm_tok, tm_wgt, tm_out, p);
-  return cudaGetLastError() == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(grid);
+  lc.blockDim = dim3(g.threads);
+  lc.dynamicSmemBytes = g.smem;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = attr;
+  lc.numAttrs = use_pdl() ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&lc, kern, tm_tok, tm_wgt, tm_out, p);
+  if (e != cudaSuccess) (void)cudaGetLastError();
+  return e == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
 }
 
 template <int UMMA_N, bool SWAP>

@@ -50,8 +50,8 @@ struct KParams {
 struct __align__(8) SharedCtl {
   unsigned long long full[kMaxStages];
   unsigned long long empty[kMaxStages];
-  unsigned long long tfull[4];    // [TMEM buffer][column half]
-  unsigned long long tempty[4];
+  unsigned long long tfull[8];    // one per TMEM accumulator buffer
+  unsigned long long tempty[8];
   unsigned long long scfull[2];
   unsigned long long scempty[2];
   unsigned int tmem_base;
@@ -131,7 +131,10 @@ struct KernelTraits {
   static constexpr uint32_t ROW_BYTES = 128u * 128u;
   static constexpr uint32_t COL_BYTES = UMMA_N * 128u;
   static constexpr uint32_t STAGE_BYTES = ROW_BYTES + COL_BYTES;
-  static constexpr uint32_t TMEM_COLS = 2 * UMMA_N < 32 ? 32 : 2 * UMMA_N;
+  // TMEM accumulator buffers: two for wide tiles (all 512 columns at UMMA_N = 256); narrow
+  // tiles get more, so that the MMAs of a short K range never wait for promotion.
+  static constexpr int NBUF = UMMA_N >= 128 ? 2 : (UMMA_N == 64 ? 4 : 8);
+  static constexpr uint32_t TMEM_COLS = NBUF * UMMA_N < 32 ? 32 : NBUF * UMMA_N;
   // A K-block partial can be produced and consumed as independent column halves (own MMAs,
   // own barriers).  Measured slower: every tcgen05.commit costs the issuing thread ~250
   // cycles, and halves double the commits.  Kept at 1.
@@ -150,7 +153,8 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   using T = KernelTraits<UMMA_N, SWAP>;
   constexpr int NPW = T::NPW, CPT = T::CPT, CH = T::CH, NCH = T::NCH, TT = T::TT, WT = T::WT;
   constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES, ROW_BYTES = T::ROW_BYTES;
-  constexpr int HALVES = T::HALVES, NH = T::NH;
+  constexpr int HALVES = T::HALVES, NH = T::NH, NBUF = T::NBUF;
+  static_assert(HALVES == 1, "one barrier pair per TMEM buffer");
   constexpr uint32_t IDESC = ptx::idesc_f8_m128(NH);
 
   extern __shared__ unsigned char smem_raw[];
@@ -183,9 +187,9 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       ptx::mbar_init(bar_full + 8 * s, 1);
       ptx::mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int b = 0; b < 4; ++b) {
+    for (int b = 0; b < NBUF; ++b) {
       ptx::mbar_init(bar_tfull + 8 * b, 1);
-      ptx::mbar_init(bar_tempty + 8 * b, NPW / HALVES);
+      ptx::mbar_init(bar_tempty + 8 * b, NPW);
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(bar_scfull + 8 * b, 64);
@@ -206,6 +210,13 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
+
+  // Programmatic dependent launch: everything above touched only this CTA's shared memory and
+  // TMEM, so it may overlap the tail of the previous kernel in the stream.  From here on
+  // global memory is read and written: wait for the previous grid to finish and flush, then
+  // let the next grid in the stream start its own prologue early.
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
 
   BoundedWait bw{&ctl->abort, p.status, p.timeout_ns};
 
@@ -245,13 +256,13 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       bool ok = true;
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
         for (int kb = 0; kb < kbn; ++kb, ++it) {
-          const uint32_t buf = it & 1u, tph = (it >> 1) & 1u;
+          const uint32_t buf = it % NBUF, tph = (it / NBUF) & 1u;
           if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
           const uint32_t a_addr = ring + stage * STAGE_BYTES;
           const uint64_t a_desc = ptx::smem_desc_k128(a_addr);
 #pragma unroll
           for (uint32_t h = 0; h < (uint32_t)HALVES; ++h) {
-            const uint32_t tb_idx = buf * 2 + h;
+            const uint32_t tb_idx = buf;
             if (!bw.wait(bar_tempty + 8 * tb_idx, tph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
             ptx::tc_fence_after();
             const uint64_t b_desc = ptx::smem_desc_k128(a_addr + ROW_BYTES + h * NH * 128);
@@ -347,11 +358,11 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
 
       for (int kb = 0; kb < kbn && ok; ++kb, ++it) {
-        const uint32_t buf = it & 1u, tph = (it >> 1) & 1u;
+        const uint32_t buf = it % NBUF, tph = (it / NBUF) & 1u;
         float sc = 0.f;
         if (!SWAP) sc = ta[kb * TT + row] * tb[kb * 2 + half];
         const float4* sv = reinterpret_cast<const float4*>(ta + kb * TT + half * 128);
-        const uint32_t tb_idx = buf * 2 + (HALVES == 2 ? half : 0);
+        const uint32_t tb_idx = buf;
         if (!bw.wait(bar_tfull + 8 * tb_idx, tph, kWaitPromoTmemFull)) { ok = false; break; }
         // the MMAs of this K block have retired, so its operand tiles may be overwritten
         if (leader) ptx::mbar_arrive(bar_empty + 8 * pstage);
@@ -417,17 +428,18 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         if (verdict == 2) break;
         if (verdict == 0) continue;
         __threadfence();
+        constexpr int RB = CPT == 64 ? 32 : 16;   // loads per batch
         const float* base = p.ws_partial + (size_t)c.tile * p.split * tile_floats;
         for (int s = 0; s < p.split; ++s) {
           const float* src = base + s * tile_floats + (size_t)(half * 128) * 128 + row;
 #pragma unroll
-          for (int j0 = 0; j0 < CPT; j0 += 16) {
-            float v[16];
+          for (int j0 = 0; j0 < CPT; j0 += RB) {
+            float v[RB];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = __ldcg(src + (size_t)(j0 + i) * 128);
+            for (int i = 0; i < RB; ++i) v[i] = __ldcg(src + (size_t)(j0 + i) * 128);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[j0 + i] = (s == 0) ? v[i] : acc[j0 + i] + v[i];
-            asm volatile("" ::: "memory");  // keep at most 16 loads in flight per thread
+            for (int i = 0; i < RB; ++i) acc[j0 + i] = (s == 0) ? v[i] : acc[j0 + i] + v[i];
+            asm volatile("" ::: "memory");  // bound the loads in flight per thread (registers)
           }
         }
         if (leader) atomicExch(p.ws_counter + c.tile, 0);
