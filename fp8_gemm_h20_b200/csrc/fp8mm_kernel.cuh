@@ -428,18 +428,42 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         if (verdict == 2) break;
         if (verdict == 0) continue;
         __threadfence();
-        constexpr int RB = CPT == 64 ? 32 : 16;   // loads per batch
-        const float* base = p.ws_partial + (size_t)c.tile * p.split * tile_floats;
-        for (int s = 0; s < p.split; ++s) {
-          const float* src = base + s * tile_floats + (size_t)(half * 128) * 128 + row;
+        const float* base = p.ws_partial + (size_t)c.tile * p.split * tile_floats +
+                            (size_t)(half * 128) * 128 + row;
+        if constexpr (CPT <= 32) {
+          // narrow tiles: the loads of up to 64/CPT splits are in flight together (one L2 round
+          // trip instead of one per split); the additions still run in split order
+          constexpr int SG = 64 / CPT;
+          for (int s0 = 0; s0 < p.split; s0 += SG) {
+            float v[SG][CPT];
 #pragma unroll
-          for (int j0 = 0; j0 < CPT; j0 += RB) {
-            float v[RB];
+            for (int ss = 0; ss < SG; ++ss) {
+              if (s0 + ss < p.split) {
 #pragma unroll
-            for (int i = 0; i < RB; ++i) v[i] = __ldcg(src + (size_t)(j0 + i) * 128);
+                for (int j = 0; j < CPT; ++j) v[ss][j] = __ldcg(base + (size_t)(s0 + ss) * tile_floats + j * 128);
+              }
+            }
 #pragma unroll
-            for (int i = 0; i < RB; ++i) acc[j0 + i] = (s == 0) ? v[i] : acc[j0 + i] + v[i];
-            asm volatile("" ::: "memory");  // bound the loads in flight per thread (registers)
+            for (int ss = 0; ss < SG; ++ss) {
+              if (s0 + ss < p.split) {
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) acc[j] = (s0 + ss == 0) ? v[ss][j] : acc[j] + v[ss][j];
+              }
+            }
+          }
+        } else {
+          constexpr int RB = CPT == 64 ? 32 : 16;   // loads per batch
+          for (int s = 0; s < p.split; ++s) {
+            const float* src = base + s * tile_floats;
+#pragma unroll
+            for (int j0 = 0; j0 < CPT; j0 += RB) {
+              float v[RB];
+#pragma unroll
+              for (int i = 0; i < RB; ++i) v[i] = __ldcg(src + (size_t)(j0 + i) * 128);
+#pragma unroll
+              for (int i = 0; i < RB; ++i) acc[j0 + i] = (s == 0) ? v[i] : acc[j0 + i] + v[i];
+              asm volatile("" ::: "memory");  // bound the loads in flight per thread (registers)
+            }
           }
         }
         if (leader) atomicExch(p.ws_counter + c.tile, 0);
