@@ -89,7 +89,7 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   size_t smem = fixed + stages * stage_bytes;
   // Shared memory share >= TMEM share, so that CTAs that fit on an SM together (this
   // kernel's or another stream's) can never ask for more than the 512 TMEM columns.
-  const int nbuf = g->umma_n >= 128 ? 2 : (g->umma_n == 64 ? 4 : 8);   // KernelTraits::NBUF
+  const int nbuf = g->umma_n == 256 ? 2 : (g->umma_n >= 64 ? 4 : 8);   // KernelTraits::NBUF
   const size_t tmem_cols = nbuf * g->umma_n < 32 ? 32 : (size_t)nbuf * g->umma_n;
   const size_t floor_smem = tmem_cols * 456 - 1024;  // (smem + 1 KB reserved) / 228 KB >= cols / 512
   if (smem < floor_smem) smem = floor_smem;
