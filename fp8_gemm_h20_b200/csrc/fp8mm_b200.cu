@@ -73,21 +73,18 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   // So does a split over more tiles than the counter region holds (it could not pay off).
   g->split = (c->split > 1 && g->kb_total % c->split == 0 && g->tiles <= kMaxSplitTiles) ? c->split : 1;
   g->kbn = g->kb_total / g->split;
-  const int npw = g->umma_n == 256 ? 8 : 4;
+  const int npw = g->umma_n >= 128 ? 8 : 4;
   g->threads = kProducerThreads + npw * 32;
   const size_t stage_bytes = 128 * 128 + (size_t)g->umma_n * 128;
   const size_t tab_bytes = 2 * (size_t)g->kbn * g->tt * sizeof(float) + 2 * (size_t)g->kbn * 2 * sizeof(float);
   const size_t staging = g->swap ? 0 : (size_t)npw * 4096;   // bf16 output staging for TMA stores
   const size_t fixed = 1024 + staging + tab_bytes + sizeof(SharedCtl);
-  // K blocks are committed and released in groups of `group` (KernelTraits::G): the ring must
-  // hold at least one whole group (two let the TMA run ahead of the MMAs).
-  const int group = (g->umma_n == 256 ? 2 : (g->umma_n >= 64 ? 4 : 8)) / 2;
+  if (fixed + 2 * stage_bytes > kMaxDynSmem) return FP8MM_E_CONFIG;
   int stages = c->stages > 0 ? c->stages : 4;
-  if (stages < group) stages = group;
   const int fit = (int)((kMaxDynSmem - fixed) / stage_bytes);
   if (stages > fit) stages = fit;
   if (stages > kMaxStages) stages = kMaxStages;
-  if (stages < 2 || stages < group) return FP8MM_E_CONFIG;
+  if (stages < 2) return FP8MM_E_CONFIG;
   g->stages = stages;
   size_t smem = fixed + stages * stage_bytes;
   // Shared memory share >= TMEM share, so that CTAs that fit on an SM together (this

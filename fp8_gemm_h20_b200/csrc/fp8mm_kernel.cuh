@@ -5,14 +5,13 @@
 // One CTA owns one SM and walks a list of work units (output tile x K-split).
 // Roles, by warp:
 //   warp 0      TMA producer   – streams 128-byte-wide operand tiles into a shared-memory ring
-//   warp 1      MMA issuer     – per 128-wide K block: four tcgen05.mma (K=32 each) into its own
-//                                TMEM accumulator buffer, fresh accumulator every block; one
-//                                tcgen05.commit per group of 1, 2 or 4 blocks
+//   warp 1      MMA issuer     – per 128-wide K block: four tcgen05.mma (K=32 each) into one of
+//                                two TMEM accumulator buffers, fresh accumulator every block
 //   warps 2-3   scale loader   – stages the activation/weight scales of the unit in shared memory
 //   warps 4..   promotion      – tcgen05.ld the finished K block, acc += d * (As*Bs) in FP32
 //                                registers, release the TMEM buffer, finally write bf16 (or the
 //                                split-K partial) to global memory
-// Promotion of one group of K blocks overlaps the MMAs of the next through two buffer groups.
+// Promotion of K block k overlaps the MMA of block k+1 through the two TMEM buffers.
 //
 // The 128 UMMA rows (= TMEM lanes) carry tokens (SWAP=false) or weight rows (SWAP=true, for
 // small token counts); the UMMA-N columns carry the other operand.  The math follows the
@@ -51,8 +50,8 @@ struct KParams {
 struct __align__(8) SharedCtl {
   unsigned long long full[kMaxStages];
   unsigned long long empty[kMaxStages];
-  unsigned long long tfull[2];    // one per group of TMEM accumulator buffers
-  unsigned long long tempty[2];
+  unsigned long long tfull[8];    // one per TMEM accumulator buffer
+  unsigned long long tempty[8];
   unsigned long long scfull[2];
   unsigned long long scempty[2];
   unsigned int tmem_base;
@@ -122,7 +121,7 @@ __device__ __forceinline__ UnitCoord decode_unit(int u, const KParams& p) {
 
 template <int UMMA_N, bool SWAP>
 struct KernelTraits {
-  static constexpr int NPW = UMMA_N == 256 ? 8 : 4;           // promotion warps
+  static constexpr int NPW = UMMA_N >= 128 ? 8 : 4;           // promotion warps (two column halves when 8)
   static constexpr int CPT = UMMA_N / (NPW / 4);              // accumulator columns per thread
   static constexpr int CH = CPT >= 32 ? 32 : 16;              // columns per tcgen05.ld
   static constexpr int NCH = CPT / CH;
@@ -132,13 +131,17 @@ struct KernelTraits {
   static constexpr uint32_t ROW_BYTES = 128u * 128u;
   static constexpr uint32_t COL_BYTES = UMMA_N * 128u;
   static constexpr uint32_t STAGE_BYTES = ROW_BYTES + COL_BYTES;
-  // TMEM accumulator buffers, used as two groups of G.  A tcgen05.commit costs the issuing
-  // thread ~250 cycles and one commit -> promote -> release round trip ~1000, so K blocks are
-  // committed, promoted and released G at a time wherever TMEM has room: two groups of one
-  // 256-column buffer, of two 128-column buffers, of two 64-column or four narrower buffers.
+  // TMEM accumulator buffers, each with its own full/empty barrier pair.  One commit ->
+  // promote -> release round trip costs about as much as two 128x256 K blocks of MMA, so the
+  // ring should be deep: two buffers is all a 256-column tile can have (512 TMEM columns),
+  // 128- and 64-column tiles get four, narrower ones eight.
   static constexpr int NBUF = UMMA_N == 256 ? 2 : (UMMA_N >= 64 ? 4 : 8);
-  static constexpr int G = NBUF / 2;
   static constexpr uint32_t TMEM_COLS = NBUF * UMMA_N < 32 ? 32 : NBUF * UMMA_N;
+  // A K-block partial can be produced and consumed as independent column halves (own MMAs,
+  // own barriers).  Measured slower: every tcgen05.commit costs the issuing thread ~250
+  // cycles, and halves double the commits.  Kept at 1.
+  static constexpr int HALVES = 1;
+  static constexpr int NH = UMMA_N / HALVES;                  // N of one tcgen05.mma
   // bf16 output staging for TMA stores (token-major tiles): 32 rows x 64 columns per warp
   static constexpr uint32_t STAGING_BYTES = SWAP ? 0u : NPW * 4096u;
   static_assert(SWAP || UMMA_N >= 128, "token-major tiles carry 128 or 256 weight rows");
@@ -152,8 +155,9 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   using T = KernelTraits<UMMA_N, SWAP>;
   constexpr int NPW = T::NPW, CPT = T::CPT, CH = T::CH, NCH = T::NCH, TT = T::TT, WT = T::WT;
   constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES, ROW_BYTES = T::ROW_BYTES;
-  constexpr int G = T::G;
-  constexpr uint32_t IDESC = ptx::idesc_f8_m128(UMMA_N);
+  constexpr int HALVES = T::HALVES, NH = T::NH, NBUF = T::NBUF;
+  static_assert(HALVES == 1, "one barrier pair per TMEM buffer");
+  constexpr uint32_t IDESC = ptx::idesc_f8_m128(NH);
 
   extern __shared__ unsigned char smem_raw[];
   // Operand tiles need 1024-byte alignment for the 128-byte swizzle.
@@ -185,9 +189,11 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       ptx::mbar_init(bar_full + 8 * s, 1);
       ptx::mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < NBUF; ++b) {
       ptx::mbar_init(bar_tfull + 8 * b, 1);
       ptx::mbar_init(bar_tempty + 8 * b, NPW);
+    }
+    for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(bar_scfull + 8 * b, 64);
       ptx::mbar_init(bar_scempty + 8 * b, NPW);
     }
@@ -219,7 +225,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   // 384-thread variants: the four service warps hand registers to the eight promotion
   // warps, which hold 128 accumulators plus two TMEM load buffers each.
   if (warp < 4) {
-  if constexpr (NPW == 8) ptx::setmaxnreg_dec<64>();
+  if constexpr (CPT == 128) ptx::setmaxnreg_dec<64>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -251,29 +257,29 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       uint32_t ph = 0, it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
-        for (int g0 = 0; g0 < kbn && ok; g0 += G, ++it) {
-          // group `it` of up to G K blocks goes to TMEM buffers grp*G .. grp*G+G-1
-          const uint32_t grp = it & 1u, gph = (it >> 1) & 1u;
-          const int gcount = min(G, kbn - g0);
-          if (!bw.wait(bar_tempty + 8 * grp, gph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
-          for (int i = 0; i < gcount; ++i) {
-            if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
+        for (int kb = 0; kb < kbn; ++kb, ++it) {
+          const uint32_t buf = it % NBUF, tph = (it / NBUF) & 1u;
+          if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
+          const uint32_t a_addr = ring + stage * STAGE_BYTES;
+          const uint64_t a_desc = ptx::smem_desc_k128(a_addr);
+#pragma unroll
+          for (uint32_t h = 0; h < (uint32_t)HALVES; ++h) {
+            const uint32_t tb_idx = buf;
+            if (!bw.wait(bar_tempty + 8 * tb_idx, tph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
             ptx::tc_fence_after();
-            const uint32_t a_addr = ring + stage * STAGE_BYTES;
-            const uint64_t a_desc = ptx::smem_desc_k128(a_addr);
-            const uint64_t b_desc = ptx::smem_desc_k128(a_addr + ROW_BYTES);
-            const uint32_t d_tmem = tmem_base + (grp * G + i) * UMMA_N;
+            const uint64_t b_desc = ptx::smem_desc_k128(a_addr + ROW_BYTES + h * NH * 128);
+            const uint32_t d_tmem = tmem_base + buf * UMMA_N + h * NH;
 #pragma unroll
             for (uint32_t k = 0; k < 4; ++k) {
               // 32 fp8 = 32 bytes along K inside the swizzle span: +2 in 16-byte address units.
               ptx::umma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, k);
             }
-            if (++stage == stages) { stage = 0; ph ^= 1u; }
+            ptx::umma_commit(bar_tfull + 8 * tb_idx);  // this half's K-block partial is ready
           }
           if (!ok) break;
-          // One commit per group.  The ring slots are released by the promotion warps, which
-          // see the same completion through tfull: no second commit here.
-          ptx::umma_commit(bar_tfull + 8 * grp);
+          // No second commit for the ring slot: a tcgen05.commit costs this thread ~250 cycles.
+          // The promotion warps see the same completion (tfull) and release the slot.
+          if (++stage == stages) { stage = 0; ph ^= 1u; }
         }
       }
     }
@@ -333,12 +339,12 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   }
   } else {
     // ------------------------------------------------- promotion + epilogue warps
-    if constexpr (NPW == 8) ptx::setmaxnreg_inc<216>();
+    if constexpr (CPT == 128) ptx::setmaxnreg_inc<216>();
     const int pw = warp - 4;
     const int q = warp & 3;      // TMEM lane quarter this warp may read
     const int half = pw >> 2;    // which 128-column half of a 256-wide tile
     const int row = q * 32 + lane;
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * 128;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * CPT;
     const bool leader = threadIdx.x == kProducerThreads;
     uint32_t ui = 0, it = 0;
     int pstage = 0;              // ring slot of the K block being promoted
@@ -353,77 +359,48 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
 #pragma unroll
       for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
 
-// acc[ch*CH + i] += d[i] * scale for one tcgen05.ld worth of columns of K block `kb_`
-#define FP8MM_PROMOTE_CHUNK(dd_, ch_, kb_)                                                         \
-  do {                                                                                             \
-    if (SWAP) {                                                                                    \
-      const float4* sv_ = reinterpret_cast<const float4*>(ta + (kb_) * TT + half * 128);           \
-      _Pragma("unroll") for (int i_ = 0; i_ < CH; i_ += 4) {                                       \
-        const float4 s4_ = sv_[((ch_) * CH + i_) >> 2];                                            \
-        acc[(ch_) * CH + i_ + 0] = fmaf(__uint_as_float(dd_[i_ + 0]), s4_.x, acc[(ch_) * CH + i_ + 0]); \
-        acc[(ch_) * CH + i_ + 1] = fmaf(__uint_as_float(dd_[i_ + 1]), s4_.y, acc[(ch_) * CH + i_ + 1]); \
-        acc[(ch_) * CH + i_ + 2] = fmaf(__uint_as_float(dd_[i_ + 2]), s4_.z, acc[(ch_) * CH + i_ + 2]); \
-        acc[(ch_) * CH + i_ + 3] = fmaf(__uint_as_float(dd_[i_ + 3]), s4_.w, acc[(ch_) * CH + i_ + 3]); \
-      }                                                                                            \
-    } else {                                                                                       \
-      const float sc_ = ta[(kb_) * TT + row] * tb[(kb_) * 2 + half];                               \
-      _Pragma("unroll") for (int i_ = 0; i_ < CH; ++i_)                                            \
-        acc[(ch_) * CH + i_] = fmaf(__uint_as_float(dd_[i_]), sc_, acc[(ch_) * CH + i_]);          \
-    }                                                                                              \
-  } while (0)
-// every tcgen05.ld of this warp into the group has completed: hand the buffers back before
-// the remaining FMAs so that the next MMAs into them can be issued as early as possible
-#define FP8MM_RELEASE_GROUP()                                        \
-  do {                                                               \
-    ptx::tc_fence_before();                                          \
-    __syncwarp();                                                    \
-    if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * grp);           \
-  } while (0)
-
-      for (int g0 = 0; g0 < kbn && ok; g0 += G, ++it) {
-        const uint32_t grp = it & 1u, gph = (it >> 1) & 1u;
-        const int gcount = min(G, kbn - g0);
-        if (!bw.wait(bar_tfull + 8 * grp, gph, kWaitPromoTmemFull)) { ok = false; break; }
-        // the MMAs of these K blocks have retired, so their operand tiles may be overwritten
-        for (int i = 0; i < gcount; ++i) {
-          if (leader) ptx::mbar_arrive(bar_empty + 8 * pstage);
-          if (++pstage == stages) pstage = 0;
-        }
+      for (int kb = 0; kb < kbn && ok; ++kb, ++it) {
+        const uint32_t buf = it % NBUF, tph = (it / NBUF) & 1u;
+        float sc = 0.f;
+        if (!SWAP) sc = ta[kb * TT + row] * tb[kb * 2 + (half * CPT) / 128];
+        const float4* sv = reinterpret_cast<const float4*>(ta + kb * TT + half * CPT);
+        const uint32_t tb_idx = buf;
+        if (!bw.wait(bar_tfull + 8 * tb_idx, tph, kWaitPromoTmemFull)) { ok = false; break; }
+        // the MMAs of this K block have retired, so its operand tiles may be overwritten
+        if (leader) ptx::mbar_arrive(bar_empty + 8 * pstage);
+        if (++pstage == stages) pstage = 0;
         ptx::tc_fence_after();
-        const uint32_t gaddr = lane_base + grp * G * UMMA_N;
-        if constexpr (NCH == 1) {
-          // narrow tiles: the loads of the whole group are in flight together, one wait
-          uint32_t d[G][CH];
+        const uint32_t taddr = lane_base + buf * UMMA_N;
+        uint32_t d[2][CH];
+        ptx::tmem_ld<CH>(taddr, d[0]);
 #pragma unroll
-          for (int i = 0; i < G; ++i)
-            if (i < gcount) ptx::tmem_ld<CH>(gaddr + i * UMMA_N, d[i]);
+        for (int ch = 0; ch < NCH; ++ch) {
           ptx::tmem_wait_ld();
-          FP8MM_RELEASE_GROUP();
+          if (ch + 1 < NCH) {
+            ptx::tmem_ld<CH>(taddr + (ch + 1) * CH, d[(ch + 1) & 1]);
+          } else {
+            // every tcgen05.ld of this warp has completed: hand the buffer back before the
+            // last FMAs so the next MMA into it can be issued as early as possible
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * tb_idx);
+          }
+          if (SWAP) {
 #pragma unroll
-          for (int i = 0; i < G; ++i)
-            if (i < gcount) FP8MM_PROMOTE_CHUNK(d[i], 0, g0 + i);
-        } else {
-#pragma unroll
-          for (int i = 0; i < G; ++i) {
-            if (i >= gcount) break;
-            const uint32_t taddr = gaddr + i * UMMA_N;
-            uint32_t d[2][CH];
-            ptx::tmem_ld<CH>(taddr, d[0]);
-#pragma unroll
-            for (int ch = 0; ch < NCH; ++ch) {
-              ptx::tmem_wait_ld();
-              if (ch + 1 < NCH) {
-                ptx::tmem_ld<CH>(taddr + (ch + 1) * CH, d[(ch + 1) & 1]);
-              } else if (i == gcount - 1) {
-                FP8MM_RELEASE_GROUP();
-              }
-              FP8MM_PROMOTE_CHUNK(d[ch & 1], ch, g0 + i);
+            for (int i = 0; i < CH; i += 4) {
+              const float4 s4 = sv[(ch * CH + i) >> 2];
+              acc[ch * CH + i + 0] = fmaf(__uint_as_float(d[ch & 1][i + 0]), s4.x, acc[ch * CH + i + 0]);
+              acc[ch * CH + i + 1] = fmaf(__uint_as_float(d[ch & 1][i + 1]), s4.y, acc[ch * CH + i + 1]);
+              acc[ch * CH + i + 2] = fmaf(__uint_as_float(d[ch & 1][i + 2]), s4.z, acc[ch * CH + i + 2]);
+              acc[ch * CH + i + 3] = fmaf(__uint_as_float(d[ch & 1][i + 3]), s4.w, acc[ch * CH + i + 3]);
             }
+          } else {
+#pragma unroll
+            for (int i = 0; i < CH; ++i)
+              acc[ch * CH + i] = fmaf(__uint_as_float(d[ch & 1][i]), sc, acc[ch * CH + i]);
           }
         }
       }
-#undef FP8MM_PROMOTE_CHUNK
-#undef FP8MM_RELEASE_GROUP
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_scempty + 8 * t);
 
@@ -433,7 +410,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         // sums all partials in split order (bit-stable) and writes the tile.
         const size_t tile_floats = (size_t)UMMA_N * 128;
         float* part = p.ws_partial + ((size_t)c.tile * p.split + c.s) * tile_floats +
-                      (size_t)(half * 128) * 128 + row;
+                      (size_t)(half * CPT) * 128 + row;
         if (ok) {
 #pragma unroll
           for (int j = 0; j < CPT; ++j) __stcg(part + j * 128, acc[j]);
@@ -454,7 +431,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         if (verdict == 0) continue;
         __threadfence();
         const float* base = p.ws_partial + (size_t)c.tile * p.split * tile_floats +
-                            (size_t)(half * 128) * 128 + row;
+                            (size_t)(half * CPT) * 128 + row;
         if constexpr (CPT <= 32) {
           // narrow tiles: the loads of up to 64/CPT splits are in flight together (one L2 round
           // trip instead of one per split); the additions still run in split order
@@ -498,7 +475,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
 
       if (SWAP) {
         const int n = c.wi * 128 + row;
-        const int m_base = c.ti * TT + half * 128;
+        const int m_base = c.ti * TT + half * CPT;
         __nv_bfloat16* dst = p.C + (long long)m_base * p.ldc + n;
         const int m_left = p.M - m_base;
 #pragma unroll
@@ -511,7 +488,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         // (128-byte rows, 16-byte chunks XOR-swizzled by row so the writes are conflict-free)
         // and one lane hands the slab to the TMA unit, which clips it at the edges of C.
         const int m0w = c.ti * 128 + q * 32;
-        const int n0 = c.wi * WT + half * 128;
+        const int n0 = c.wi * WT + half * CPT;
         if (m0w < p.M && n0 < p.N) {
           unsigned char* stg = staging_ptr + pw * 4096;
           const uint32_t stg_addr = staging + pw * 4096;
