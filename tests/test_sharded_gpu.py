@@ -1,0 +1,53 @@
+"""N-sharded layer on two real GPUs: shard GEMMs + NCCL all-gather must reproduce the 1-GPU
+result (same kernel config per shard => bit-equal columns).  Skipped on single-GPU boxes."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    from fp8_gemm_h20_b200 import engine, sharded, testing
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        ok = True
+        for m, n, k in [(37, 1024, 512), (300, 2048, 1024)]:
+            A, B, As, Bs = (t.cuda() for t in testing.make_problem(m, n, k, seed=9))
+            conf = ("umma_swap", dict(BLOCK_T=64, SPLIT=2)) if m <= 64 else ("umma", dict(BLOCK_W=128))
+            gemm = lambda a, b, sa, sb, out: engine.launch(a, b, sa, sb, conf[0], conf[1], out=out)
+            layer = sharded.ColumnParallelFP8Linear(B, Bs, gemm=gemm)
+            out = layer(A, As)
+            full = engine.launch(A, B, As, Bs, *conf)
+            ref = testing.reference_fp32(A, B, As, Bs)
+            ok = ok and torch.equal(out, full) and testing.rel_error(out, ref) <= 1e-2
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_gather_equals_single_gpu_result():
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    assert dict(q.get(timeout=5) for _ in range(2)) == {0: True, 1: True}
