@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the GEMM kernels use:
-// mbarrier, TMA (cp.async.bulk.tensor, never multicast), tcgen05 (TMEM
+// mbarrier, TMA (cp.async.bulk.tensor, plain single-CTA loads and stores only), tcgen05 (TMEM
 // allocation, MMA, commit, load) and the matching fences.
 #pragma once
 #include <cstdint>
