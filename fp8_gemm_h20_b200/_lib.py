@@ -16,6 +16,7 @@ LIB_PATH = _PKG / LIB_NAME
 
 IMPL_UMMA = 0
 IMPL_UMMA_SWAP = 1
+IMPL_UMMA_2CTA = 2
 E_DEVICE_TIMEOUT = -8
 E_TOO_LARGE = -9
 

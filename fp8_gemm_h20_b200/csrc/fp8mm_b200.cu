@@ -13,6 +13,7 @@
 
 #include "../../include/fp8mm_b200.h"
 #include "fp8mm_kernel.cuh"
+#include "fp8mm_kernel_2cta.cuh"
 
 namespace fp8mm {
 namespace {
@@ -29,6 +30,7 @@ constexpr int kMaxDevices = 64;
 struct Geometry {
   int umma_n;       // UMMA N = columns of the accumulator tile
   bool swap;
+  bool pair;        // CTA pairs (cta_group::2): 256 tokens per tile, each CTA loads half of B
   int tt, wt;       // token / weight tile
   int t_tiles, w_tiles, tiles;
   int kb_total, split, kbn;
@@ -51,6 +53,8 @@ int check_cfg(int M, int N, int K, const fp8mm_cfg* c) {
   } else if (c->impl == FP8MM_IMPL_UMMA_SWAP) {
     if (c->block_w != 128) return FP8MM_E_CONFIG;
     if (!is_pow2(c->block_t) || c->block_t < 16 || c->block_t > 256) return FP8MM_E_CONFIG;
+  } else if (c->impl == FP8MM_IMPL_UMMA_2CTA) {
+    if (c->block_t != 256 || c->block_w != 256) return FP8MM_E_CONFIG;
   } else {
     return FP8MM_E_CONFIG;
   }
@@ -62,6 +66,7 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   const int rc = check_cfg(M, N, K, c);
   if (rc != FP8MM_OK) return rc;
   g->swap = c->impl == FP8MM_IMPL_UMMA_SWAP;
+  g->pair = c->impl == FP8MM_IMPL_UMMA_2CTA;
   g->umma_n = g->swap ? c->block_t : c->block_w;
   g->tt = c->block_t;
   g->wt = c->block_w;
@@ -71,16 +76,18 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   g->kb_total = K / 128;
   // A split that does not divide the K-block count runs unsplit (kernel_v2.py:355-356).
   // So does a split over more tiles than the counter region holds (it could not pay off).
-  g->split = (c->split > 1 && g->kb_total % c->split == 0 && g->tiles <= kMaxSplitTiles) ? c->split : 1;
+  g->split = (c->split > 1 && g->kb_total % c->split == 0 && g->tiles <= kMaxSplitTiles && !g->pair)
+                 ? c->split : 1;
   g->kbn = g->kb_total / g->split;
   const int npw = g->umma_n >= 128 ? 8 : 4;
   g->threads = kProducerThreads + npw * 32;
-  const size_t stage_bytes = 128 * 128 + (size_t)g->umma_n * 128;
-  const size_t tab_bytes = 2 * (size_t)g->kbn * g->tt * sizeof(float) + 2 * (size_t)g->kbn * 2 * sizeof(float);
+  const size_t stage_bytes = g->pair ? 2 * 128 * 128 : 128 * 128 + (size_t)g->umma_n * 128;
+  const size_t tab_rows = g->pair ? 128 : g->tt;    // token rows per CTA in the scale table
+  const size_t tab_bytes = 2 * (size_t)g->kbn * tab_rows * sizeof(float) + 2 * (size_t)g->kbn * 2 * sizeof(float);
   const size_t staging = g->swap ? 0 : (size_t)npw * 4096;   // bf16 output staging for TMA stores
   const size_t fixed = 1024 + staging + tab_bytes + sizeof(SharedCtl);
   if (fixed + 2 * stage_bytes > kMaxDynSmem) return FP8MM_E_CONFIG;
-  int stages = c->stages > 0 ? c->stages : 4;
+  int stages = c->stages > 0 ? c->stages : (g->pair ? 5 : 4);
   const int fit = (int)((kMaxDynSmem - fixed) / stage_bytes);
   if (stages > fit) stages = fit;
   if (stages > kMaxStages) stages = kMaxStages;
@@ -239,6 +246,33 @@ int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, 
   return e == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
 }
 
+int launch_pair(int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
+                const CUtensorMap& tm_out, const KParams& p, int grid, cudaStream_t stream) {
+  auto kern = fp8mm_umma_2cta_kernel;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_dev[dev].attr_set[31]) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem) !=
+          cudaSuccess)
+        return FP8MM_E_LAUNCH;
+      g_dev[dev].attr_set[31] = true;
+    }
+  }
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(grid);
+  lc.blockDim = dim3(g.threads);
+  lc.dynamicSmemBytes = g.smem;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = attr;
+  lc.numAttrs = use_pdl() ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&lc, kern, tm_tok, tm_wgt, tm_out, p);
+  if (e != cudaSuccess) (void)cudaGetLastError();
+  return e == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
+}
+
 template <int UMMA_N, bool SWAP>
 int launch(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
            const CUtensorMap& tm_out, const KParams& p, int grid, cudaStream_t stream) {
@@ -337,7 +371,7 @@ int fp8mm_b200_gemm(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace, 
   CUtensorMap tm_tok, tm_wgt;
   rc = get_tensor_map(a->A, a->M, a->K, g.swap ? g.umma_n : 128, &tm_tok);
   if (rc != FP8MM_OK) return rc;
-  rc = get_tensor_map(a->B, a->N, a->K, g.swap ? 128 : g.umma_n, &tm_wgt);
+  rc = get_tensor_map(a->B, a->N, a->K, (g.swap || g.pair) ? 128 : g.umma_n, &tm_wgt);
   if (rc != FP8MM_OK) return rc;
 
   CUtensorMap tm_out;
@@ -382,6 +416,13 @@ int fp8mm_b200_gemm(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace, 
   if (grid > p.num_units) grid = p.num_units;
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (g.pair) {
+    // one CTA pair per two SMs; the grid is a whole number of pairs
+    int pairs = g_dev[dev].sms / 2;
+    if (cfg->max_ctas > 0 && pairs > cfg->max_ctas / 2) pairs = cfg->max_ctas / 2 > 0 ? cfg->max_ctas / 2 : 1;
+    if (pairs > p.num_units) pairs = p.num_units;
+    return launch_pair(dev, g, tm_tok, tm_wgt, tm_out, p, 2 * pairs, stream);
+  }
   if (g.swap) {
     switch (g.umma_n) {
       case 16: return launch<16, true>(0, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);

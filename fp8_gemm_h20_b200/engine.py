@@ -16,6 +16,8 @@ from . import _lib
 KERNELS = {
     "umma": (_lib.IMPL_UMMA, {"BLOCK_T": 128, "BLOCK_W": 256, "NUM_STAGES": 4, "SPLIT": 1,
                               "GROUP_SIZE_M": 8, "MAX_CTAS": 0}),
+    "umma_2cta": (_lib.IMPL_UMMA_2CTA, {"BLOCK_T": 256, "BLOCK_W": 256, "NUM_STAGES": 5, "SPLIT": 1,
+                                        "GROUP_SIZE_M": 8, "MAX_CTAS": 0}),
     "umma_swap": (_lib.IMPL_UMMA_SWAP, {"BLOCK_T": 16, "BLOCK_W": 128, "NUM_STAGES": 8, "SPLIT": 1,
                                         "GROUP_SIZE_M": 1, "MAX_CTAS": 0}),
 }

@@ -41,6 +41,7 @@ extern "C" {
 /* ---- kernel families ("impl" names of the JSON tuning tables) ------------ */
 #define FP8MM_IMPL_UMMA        0    /* tokens on the 128 UMMA rows, weights on UMMA-N (128|256)  */
 #define FP8MM_IMPL_UMMA_SWAP   1    /* swap-AB: weights on the 128 UMMA rows, tokens on UMMA-N   */
+#define FP8MM_IMPL_UMMA_2CTA   2    /* CTA pairs (cta_group::2): 256 tokens x 256 weights per pair */
 
 /*
  * Operands.  Strides are in ELEMENTS and are exactly the values the reference
@@ -69,8 +70,8 @@ typedef struct fp8mm_args {
 /*
  * Launch configuration = one "config" object of a tuning-table entry
  * (fp8_gemm_h20/configs/*.json, "entries"/"N,K"/"M"/{"impl","config"}).
- *   block_t   token tile   (BLOCK_T):  UMMA   -> 128;  UMMA_SWAP -> 16,32,64,128,256
- *   block_w   weight tile  (BLOCK_W):  UMMA   -> 128 or 256;  UMMA_SWAP -> 128
+ *   block_t   token tile   (BLOCK_T):  UMMA   -> 128;  UMMA_SWAP -> 16,32,64,128,256;  UMMA_2CTA -> 256
+ *   block_w   weight tile  (BLOCK_W):  UMMA   -> 128 or 256;  UMMA_SWAP -> 128;  UMMA_2CTA -> 256
  *   stages    depth of the TMA shared-memory ring (NUM_STAGES); clipped to what fits
  *   split     split-K factor (SPLIT); a value that does not divide K/128 is
  *             legalised to 1, as the reference wrapper does (kernel_v2.py:355-356)
