@@ -26,6 +26,7 @@ SYMBOLS = (
     "fp8mm_b200_workspace_bytes",
     "fp8mm_b200_workspace_init",
     "fp8mm_b200_gemm",
+    "fp8mm_b200_gemm_bcast",
     "fp8mm_b200_gemm_static_scratch",
     "fp8mm_b200_static_scratch_bytes",
     "fp8mm_b200_last_status",
@@ -85,6 +86,10 @@ def load():
         lib.fp8mm_b200_gemm.argtypes = [ctypes.POINTER(Args), ctypes.POINTER(Cfg), ctypes.c_void_p,
                                         ctypes.c_size_t, ctypes.c_void_p]
         lib.fp8mm_b200_gemm.restype = ctypes.c_int
+        lib.fp8mm_b200_gemm_bcast.argtypes = [ctypes.POINTER(Args), ctypes.POINTER(Cfg), ctypes.c_void_p,
+                                              ctypes.c_size_t, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
+                                              ctypes.c_int32]
+        lib.fp8mm_b200_gemm_bcast.restype = ctypes.c_int
         lib.fp8mm_b200_gemm_static_scratch.argtypes = [ctypes.POINTER(Args), ctypes.POINTER(Cfg), ctypes.c_void_p]
         lib.fp8mm_b200_gemm_static_scratch.restype = ctypes.c_int
         lib.fp8mm_b200_static_scratch_bytes.argtypes = []

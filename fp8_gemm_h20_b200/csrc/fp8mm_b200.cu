@@ -220,7 +220,7 @@ bool use_pdl() {
 
 template <int UMMA_N, bool SWAP, bool SPLITK>
 int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
-               const CUtensorMap& tm_out, const KParams& p, int grid, cudaStream_t stream) {
+               const OutTargets& outs, const KParams& p, int grid, cudaStream_t stream) {
   auto kern = fp8mm_umma_kernel<UMMA_N, SWAP, SPLITK>;
   {
     std::lock_guard<std::mutex> lk(g_mu);
@@ -241,13 +241,13 @@ int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = attr;
   lc.numAttrs = use_pdl() ? 1 : 0;
-  const cudaError_t e = cudaLaunchKernelEx(&lc, kern, tm_tok, tm_wgt, tm_out, p);
+  const cudaError_t e = cudaLaunchKernelEx(&lc, kern, tm_tok, tm_wgt, outs, p);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return e == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
 }
 
 int launch_pair(int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
-                const CUtensorMap& tm_out, const KParams& p, int grid, cudaStream_t stream) {
+                const OutTargets& outs, const KParams& p, int grid, cudaStream_t stream) {
   auto kern = fp8mm_umma_2cta_kernel;
   {
     std::lock_guard<std::mutex> lk(g_mu);
@@ -268,17 +268,17 @@ int launch_pair(int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUt
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = attr;
   lc.numAttrs = use_pdl() ? 1 : 0;
-  const cudaError_t e = cudaLaunchKernelEx(&lc, kern, tm_tok, tm_wgt, tm_out, p);
+  const cudaError_t e = cudaLaunchKernelEx(&lc, kern, tm_tok, tm_wgt, outs, p);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return e == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
 }
 
 template <int UMMA_N, bool SWAP>
 int launch(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
-           const CUtensorMap& tm_out, const KParams& p, int grid, cudaStream_t stream) {
+           const OutTargets& outs, const KParams& p, int grid, cudaStream_t stream) {
   if (g.split > 1)
-    return launch_one<UMMA_N, SWAP, true>(2 * slot + 1, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
-  return launch_one<UMMA_N, SWAP, false>(2 * slot, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
+    return launch_one<UMMA_N, SWAP, true>(2 * slot + 1, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+  return launch_one<UMMA_N, SWAP, false>(2 * slot, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
 }
 
 }  // namespace
@@ -344,8 +344,9 @@ int fp8mm_b200_last_status(const void* workspace, int32_t* detail) {
   return v == 0 ? FP8MM_OK : FP8MM_E_DEVICE_TIMEOUT;
 }
 
-int fp8mm_b200_gemm(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace, size_t ws_bytes,
-                    void* stream_) {
+static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace, size_t ws_bytes,
+                     void* stream_, void* const* extra_c, int n_extra) {
+  if (n_extra < 0 || n_extra > kMaxOutTargets - 1 || (n_extra > 0 && extra_c == nullptr)) return FP8MM_E_CONFIG;
   if (a == nullptr || cfg == nullptr) return FP8MM_E_NULL;
   if (a->A == nullptr || a->B == nullptr || a->As == nullptr || a->Bs == nullptr || a->C == nullptr)
     return FP8MM_E_NULL;
@@ -374,12 +375,18 @@ int fp8mm_b200_gemm(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace, 
   rc = get_tensor_map(a->B, a->N, a->K, (g.swap || g.pair) ? 128 : g.umma_n, &tm_wgt);
   if (rc != FP8MM_OK) return rc;
 
-  CUtensorMap tm_out;
-  if (g.swap) {
-    memset(&tm_out, 0, sizeof(tm_out));
-  } else {
-    rc = make_output_map(a->C, a->M, a->N, a->ldc, &tm_out);
-    if (rc != FP8MM_OK) return rc;
+  OutTargets outs;
+  memset(&outs, 0, sizeof(outs));
+  outs.n = 1 + n_extra;
+  for (int d = 0; d < outs.n; ++d) {
+    void* c = d == 0 ? a->C : extra_c[d - 1];
+    if (c == nullptr) return FP8MM_E_NULL;
+    if (reinterpret_cast<uintptr_t>(c) & 15) return FP8MM_E_ALIGN;
+    outs.ptr[d] = static_cast<__nv_bfloat16*>(c);
+    if (!g.swap) {
+      rc = make_output_map(c, a->M, a->N, a->ldc, &outs.map[d]);
+      if (rc != FP8MM_OK) return rc;
+    }
   }
 
   unsigned char* ws = static_cast<unsigned char*>(workspace);
@@ -421,23 +428,33 @@ int fp8mm_b200_gemm(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace, 
     int pairs = g_dev[dev].sms / 2;
     if (cfg->max_ctas > 0 && pairs > cfg->max_ctas / 2) pairs = cfg->max_ctas / 2 > 0 ? cfg->max_ctas / 2 : 1;
     if (pairs > p.num_units) pairs = p.num_units;
-    return launch_pair(dev, g, tm_tok, tm_wgt, tm_out, p, 2 * pairs, stream);
+    return launch_pair(dev, g, tm_tok, tm_wgt, outs, p, 2 * pairs, stream);
   }
   if (g.swap) {
     switch (g.umma_n) {
-      case 16: return launch<16, true>(0, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
-      case 32: return launch<32, true>(1, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
-      case 64: return launch<64, true>(2, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
-      case 128: return launch<128, true>(3, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
-      case 256: return launch<256, true>(4, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
+      case 16: return launch<16, true>(0, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+      case 32: return launch<32, true>(1, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+      case 64: return launch<64, true>(2, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+      case 128: return launch<128, true>(3, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+      case 256: return launch<256, true>(4, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
     }
   } else {
     switch (g.umma_n) {
-      case 128: return launch<128, false>(5, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
-      case 256: return launch<256, false>(6, dev, g, tm_tok, tm_wgt, tm_out, p, grid, stream);
+      case 128: return launch<128, false>(5, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+      case 256: return launch<256, false>(6, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
     }
   }
   return FP8MM_E_CONFIG;
+}
+
+int fp8mm_b200_gemm(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace, size_t ws_bytes,
+                    void* stream) {
+  return gemm_impl(a, cfg, workspace, ws_bytes, stream, nullptr, 0);
+}
+
+int fp8mm_b200_gemm_bcast(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace, size_t ws_bytes,
+                          void* stream, void* const* extra_c, int32_t n_extra) {
+  return gemm_impl(a, cfg, workspace, ws_bytes, stream, extra_c, n_extra);
 }
 
 // ----------------------------------------------------- allocation-free entry point

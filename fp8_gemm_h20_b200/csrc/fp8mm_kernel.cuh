@@ -47,6 +47,17 @@ struct KParams {
   int stages;
 };
 
+// Where the bf16 result goes: the caller's C and, for the fused all-gather of the N-sharded
+// layer, the same slice of every peer GPU's buffer (plain peer-to-peer stores; the TMA stores
+// are ordinary single-destination bulk copies, one per target).
+constexpr int kMaxOutTargets = 8;
+struct OutTargets {
+  CUtensorMap map[kMaxOutTargets];      // token-major tiles: one tensor map per target
+  __nv_bfloat16* ptr[kMaxOutTargets];   // swap-AB tiles: plain stores
+  int n;
+  int pad;
+};
+
 struct __align__(8) SharedCtl {
   unsigned long long full[kMaxStages];
   unsigned long long empty[kMaxStages];
@@ -151,7 +162,7 @@ template <int UMMA_N, bool SWAP, bool SPLITK>
 __global__ void __launch_bounds__(KernelTraits<UMMA_N, SWAP>::THREADS, 1)
 fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
                   const __grid_constant__ CUtensorMap tm_wgt,
-                  const __grid_constant__ CUtensorMap tm_out, const KParams p) {
+                  const __grid_constant__ OutTargets outs, const KParams p) {
   using T = KernelTraits<UMMA_N, SWAP>;
   constexpr int NPW = T::NPW, CPT = T::CPT, CH = T::CH, NCH = T::NCH, TT = T::TT, WT = T::WT;
   constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES, ROW_BYTES = T::ROW_BYTES;
@@ -202,7 +213,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tm_tok);
     ptx::prefetch_tensormap(&tm_wgt);
-    if (!SWAP) ptx::prefetch_tensormap(&tm_out);
+    if (!SWAP) for (int d = 0; d < outs.n; ++d) ptx::prefetch_tensormap(&outs.map[d]);
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(&ctl->tmem_base), T::TMEM_COLS);
@@ -476,12 +487,14 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       if (SWAP) {
         const int n = c.wi * 128 + row;
         const int m_base = c.ti * TT + half * CPT;
-        __nv_bfloat16* dst = p.C + (long long)m_base * p.ldc + n;
         const int m_left = p.M - m_base;
+        for (int d = 0; d < outs.n; ++d) {
+          __nv_bfloat16* dst = outs.ptr[d] + (long long)m_base * p.ldc + n;
 #pragma unroll
-        for (int j = 0; j < CPT; ++j) {
-          if (j < m_left) *dst = __float2bfloat16_rn(acc[j]);
-          dst += p.ldc;
+          for (int j = 0; j < CPT; ++j) {
+            if (j < m_left) *dst = __float2bfloat16_rn(acc[j]);
+            dst += p.ldc;
+          }
         }
       } else {
         // Coalesced bf16 epilogue: each warp stages its 32 rows x 64 columns in shared memory
@@ -513,14 +526,14 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              ptx::tma_store_2d(&tm_out, stg_addr, n0 + sl * 64, m0w);
+              for (int d = 0; d < outs.n; ++d) ptx::tma_store_2d(&outs.map[d], stg_addr, n0 + sl * 64, m0w);
               ptx::bulk_commit_group();
             }
           }
         }
       }
     }
-    if (!SWAP && lane == 0) ptx::bulk_wait_read_all();
+    if (!SWAP && lane == 0) ptx::bulk_wait_all();   // stores (also those to peer GPUs) are done
     __syncwarp();
   }
 

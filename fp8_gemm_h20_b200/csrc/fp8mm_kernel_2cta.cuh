@@ -1,13 +1,16 @@
 // Two-CTA (cta_group::2) variant of the block-scaled FP8 GEMM for large token counts.
 //
-// Why: with one CTA per tile every SM has to pull its whole A tile and B tile through its own
-// L2 port: 48 KB per 128x256 K block against ~512 cycles of MMA.  Measured, the port delivers
-// about 43 bytes per cycle, so operand delivery, not the tensor pipe, sets the pace.  A CTA
-// pair computes a 256 (tokens) x 256 (weights) tile with tcgen05.mma.cta_group::2: each CTA
-// loads only its own 128 token rows and its own HALF of the weight tile (32 KB per K block
+// A CTA pair computes a 256 (tokens) x 256 (weights) tile with tcgen05.mma.cta_group::2: each
+// CTA loads only its own 128 token rows and its own HALF of the weight tile (32 KB per K block
 // instead of 48 KB for the same MMA work per SM); the tensor cores read the other half of B
-// from the partner's shared memory.  No TMA multicast is involved: every load is an ordinary
-// single-destination cp.async.bulk.tensor issued by the CTA that owns the bytes.
+// from the partner's shared memory.  Every load is an ordinary single-destination
+// cp.async.bulk.tensor issued by the CTA that owns the bytes.
+//
+// Measured on B200 it is correct (bit-equal to the one-CTA 128x256 kernel) but slower,
+// 1.07 against 1.78 PFLOP/s at M=8192, N=12288, K=2048: with per-K-block promotion the pace is
+// set by the commit -> promote -> release round trip between the MMA thread and the promotion
+// warps, and across two SMs that round trip is about twice as long.  The tuning tables do not
+// select it; it stays available as impl "umma_2cta".
 //
 // Roles per CTA are those of fp8mm_umma_kernel (TMA producer, MMA issuer, scale loader, eight
 // promotion/epilogue warps).  Differences:
@@ -103,7 +106,7 @@ struct Pair2Cta {
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Pair2Cta::THREADS, 1)
 fp8mm_umma_2cta_kernel(const __grid_constant__ CUtensorMap tm_tok,
                        const __grid_constant__ CUtensorMap tm_wgt,
-                       const __grid_constant__ CUtensorMap tm_out, const KParams p) {
+                       const __grid_constant__ OutTargets outs, const KParams p) {
   using T = Pair2Cta;
   constexpr int UMMA_N = T::UMMA_N, NPW = T::NPW, CPT = T::CPT, CH = T::CH, NCH = T::NCH;
   constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES, A_BYTES = T::A_BYTES;
@@ -156,7 +159,7 @@ fp8mm_umma_2cta_kernel(const __grid_constant__ CUtensorMap tm_tok,
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tm_tok);
     ptx::prefetch_tensormap(&tm_wgt);
-    ptx::prefetch_tensormap(&tm_out);
+    for (int d = 0; d < outs.n; ++d) ptx::prefetch_tensormap(&outs.map[d]);
   }
   if (warp == 1) {
     ptx::tmem_alloc_2cta(ptx::smem_u32(&ctl->tmem_base), T::TMEM_COLS);
@@ -334,13 +337,13 @@ fp8mm_umma_2cta_kernel(const __grid_constant__ CUtensorMap tm_tok,
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            ptx::tma_store_2d(&tm_out, stg_addr, n0 + sl * 64, m0w);
+            for (int d = 0; d < outs.n; ++d) ptx::tma_store_2d(&outs.map[d], stg_addr, n0 + sl * 64, m0w);
             ptx::bulk_commit_group();
           }
         }
       }
     }
-    if (lane == 0) ptx::bulk_wait_read_all();
+    if (lane == 0) ptx::bulk_wait_all();   // stores (also those to peer GPUs) are done
     __syncwarp();
   }
 

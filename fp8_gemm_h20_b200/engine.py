@@ -53,11 +53,14 @@ def _workspace(torch, device, stream, nbytes):
     return ws
 
 
-def launch(A, B, As, Bs, impl, config, out=None):
+def launch(A, B, As, Bs, impl, config, out=None, also_to=()):
     """Enqueue C = blockscaled(A @ B^T) on the current stream of A.device and return C.
 
     `out`, when given, is a bf16 [M, N] view whose rows may be strided (row stride a
-    multiple of 8 elements): the N-sharded layer writes shards into a wider buffer."""
+    multiple of 8 elements): the N-sharded layer writes shards into a wider buffer.
+    `also_to` lists up to 7 device addresses (ints) of further buffers with the layout of
+    `out` — the peers' copies of an N-sharded layer's output — that receive the same tiles
+    from the kernel's epilogue (fused all-gather, fp8mm_b200_gemm_bcast)."""
     import torch
     lib = _lib.load()
     m, k = A.shape
@@ -77,7 +80,12 @@ def launch(A, B, As, Bs, impl, config, out=None):
                      M=m, N=n, K=k, reserved0=0,
                      as_stride_m=As.stride(0), as_stride_k=As.stride(1),
                      bs_stride_n=Bs.stride(0), bs_stride_k=Bs.stride(1), ldc=out.stride(0))
-    rc = lib.fp8mm_b200_gemm(ctypes.byref(args), ctypes.byref(cfg), ws.data_ptr(), ws.numel(), stream)
+    if also_to:
+        extra = (ctypes.c_void_p * len(also_to))(*[int(x) for x in also_to])
+        rc = lib.fp8mm_b200_gemm_bcast(ctypes.byref(args), ctypes.byref(cfg), ws.data_ptr(), ws.numel(), stream,
+                                       extra, len(also_to))
+    else:
+        rc = lib.fp8mm_b200_gemm(ctypes.byref(args), ctypes.byref(cfg), ws.data_ptr(), ws.numel(), stream)
     if rc != 0:
         raise RuntimeError(f"fp8mm_b200_gemm failed: {_lib.strerror(rc)} "
                            f"(impl={impl}, config={dict(config)}, M,N,K={m},{n},{k})")

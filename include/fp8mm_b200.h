@@ -111,6 +111,16 @@ int fp8mm_b200_workspace_init(void* workspace, size_t ws_bytes, void* stream);
 int fp8mm_b200_gemm(const fp8mm_args* args, const fp8mm_cfg* cfg,
                     void* workspace, size_t ws_bytes, void* stream);
 
+/* The same GEMM with its result also stored into up to 7 more buffers of the same shape and
+ * row stride: `extra_c[i]` are device pointers, typically the peer GPUs' copies of the output
+ * of an N-sharded (column-parallel) layer, mapped into this process (CUDA IPC / symmetric
+ * memory).  The kernel's epilogue writes every tile to args->C and to each extra target with
+ * plain peer-to-peer stores, which fuses the all-gather that would otherwise follow the GEMM.
+ * The caller orders the peers' reads after this kernel (a barrier across the ranks).
+ * No counterpart in the reference, which is single-GPU (README.md:50,74). */
+int fp8mm_b200_gemm_bcast(const fp8mm_args* args, const fp8mm_cfg* cfg, void* workspace, size_t ws_bytes,
+                          void* stream, void* const* extra_c, int32_t n_extra);
+
 /*
  * Allocation-free variant of fp8mm_b200_gemm.  No counterpart in the reference: its wrappers
  * allocate their split-K workspace with torch (kernel_v2.py:316-324) and so does the binding

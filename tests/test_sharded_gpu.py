@@ -31,6 +31,16 @@ def _worker(rank, world, port, q):
             full = engine.launch(A, B, As, Bs, *conf)
             ref = testing.reference_fp32(A, B, As, Bs)
             ok = ok and torch.equal(out, full) and testing.rel_error(out, ref) <= 1e-2
+        # fused path: the GEMM epilogue stores straight into every rank's symmetric output buffer
+        for m, n, k in [(37, 5120, 3072), (300, 5120, 3072), (2048, 4608, 3072)]:
+            A, B, As, Bs = (t.cuda() for t in testing.make_problem(m, n, k, seed=3))
+            plain = sharded.ColumnParallelFP8Linear(B, Bs)
+            fused = sharded.ColumnParallelFP8Linear(B, Bs, fused=True, max_tokens=2048)
+            want = plain(A, As)
+            for _ in range(3):                       # repeated calls reuse the symmetric buffer
+                got = fused(A, As).clone()
+                ok = ok and torch.equal(got, want)
+            ok = ok and testing.rel_error(got, testing.reference_fp32(A, B, As, Bs)) <= 1e-2
         q.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()
