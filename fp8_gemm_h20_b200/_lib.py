@@ -28,6 +28,7 @@ SYMBOLS = (
     "fp8mm_b200_gemm",
     "fp8mm_b200_gemm_bcast",
     "fp8mm_b200_gemm_static_scratch",
+    "fp8mm_b200_quantize_act",
     "fp8mm_b200_static_scratch_bytes",
     "fp8mm_b200_last_status",
     "fp8mm_b200_strerror",
@@ -92,6 +93,10 @@ def load():
         lib.fp8mm_b200_gemm_bcast.restype = ctypes.c_int
         lib.fp8mm_b200_gemm_static_scratch.argtypes = [ctypes.POINTER(Args), ctypes.POINTER(Cfg), ctypes.c_void_p]
         lib.fp8mm_b200_gemm_static_scratch.restype = ctypes.c_int
+        lib.fp8mm_b200_quantize_act.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
+                                                ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                                ctypes.c_float, ctypes.c_void_p]
+        lib.fp8mm_b200_quantize_act.restype = ctypes.c_int
         lib.fp8mm_b200_static_scratch_bytes.argtypes = []
         lib.fp8mm_b200_static_scratch_bytes.restype = ctypes.c_size_t
         lib.fp8mm_b200_last_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]

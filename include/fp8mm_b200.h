@@ -154,6 +154,16 @@ int fp8mm_b200_gemm_static_scratch(const fp8mm_args* args, const fp8mm_cfg* cfg,
 /* Size in bytes of the built-in scratch buffer used by fp8mm_b200_gemm_static_scratch. */
 size_t fp8mm_b200_static_scratch_bytes(void);
 
+/* Activation quantiser, the step in front of the GEMM: bf16 X[M,K] (row stride ldx) ->
+ * e4m3 A[M,K] (contiguous) and fp32 As[M,K/128] (any strides): per 1x128 group
+ * scale = max(amax, floor)/448, a = e4m3(clamp(x/scale, +-448)).  Stands where the reference's
+ * adapter calls SGLang's sglang_per_token_group_quant_fp8(x, 128, column_major_scales=False,
+ * scale_tma_aligned=False) (sgl_patch/fp8mm_sglang_patch.py:53); the recipe is the one of
+ * scripts/validate.py:26-28. */
+int fp8mm_b200_quantize_act(const void* x_bf16, void* a_e4m3, float* as, int32_t M, int32_t K,
+                            int64_t ldx, int64_t as_stride_m, int64_t as_stride_k, float floor_,
+                            void* stream);
+
 /* After the stream has been synchronised: 0 if no bounded device-side wait gave
  * up since the workspace was initialised, else FP8MM_E_DEVICE_TIMEOUT; *detail
  * (optional) receives the role/barrier code recorded by the kernel.  Blocking. */
