@@ -30,6 +30,7 @@ constexpr int kMaxDevices = 64;
 struct Geometry {
   int umma_n;       // UMMA N = columns of the accumulator tile
   bool swap;
+  bool cluster;     // split-K reduced through a thread-block cluster instead of the workspace
   bool pair;        // CTA pairs (cta_group::2): 256 tokens per tile, each CTA loads half of B
   int tt, wt;       // token / weight tile
   int t_tiles, w_tiles, tiles;
@@ -41,11 +42,12 @@ struct Geometry {
 };
 
 bool is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
+bool cluster_split_allowed();
 
 int check_cfg(int M, int N, int K, const fp8mm_cfg* c) {
   if (c == nullptr) return FP8MM_E_NULL;
   if (M < 1 || N < 128 || K < 128 || (N % 128) != 0 || (K % 128) != 0) return FP8MM_E_SHAPE;
-  if (c->flags != 0) return FP8MM_E_CONFIG;
+  if ((c->flags & ~FP8MM_FLAG_WORKSPACE_SPLIT) != 0) return FP8MM_E_CONFIG;
   if (c->split < 1 || c->group_m < 1 || c->stages < 0 || c->max_ctas < 0) return FP8MM_E_CONFIG;
   if (c->impl == FP8MM_IMPL_UMMA) {
     if (c->block_t != 128) return FP8MM_E_CONFIG;
@@ -79,6 +81,8 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   g->split = (c->split > 1 && g->kb_total % c->split == 0 && g->tiles <= kMaxSplitTiles && !g->pair)
                  ? c->split : 1;
   g->kbn = g->kb_total / g->split;
+  g->cluster = (g->split == 2 || g->split == 4 || g->split == 8) && cluster_split_allowed() &&
+               !(c->flags & FP8MM_FLAG_WORKSPACE_SPLIT);
   const int npw = g->umma_n >= 128 ? 8 : 4;
   g->threads = kProducerThreads + npw * 32;
   const size_t stage_bytes = g->pair ? 2 * 128 * 128 : 128 * 128 + (size_t)g->umma_n * 128;
@@ -93,6 +97,8 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return FP8MM_E_CONFIG;
   g->stages = stages;
+  // the cluster reduction parks the fp32 partial tile in the (then idle) operand ring
+  if (g->cluster && (size_t)stages * stage_bytes < (size_t)g->umma_n * 128 * sizeof(float)) g->cluster = false;
   size_t smem = fixed + stages * stage_bytes;
   // Shared memory share >= TMEM share, so that CTAs that fit on an SM together (this
   // kernel's or another stream's) can never ask for more than the 512 TMEM columns.
@@ -101,8 +107,9 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   const size_t floor_smem = tmem_cols * 456 - 1024;  // (smem + 1 KB reserved) / 228 KB >= cols / 512
   if (smem < floor_smem) smem = floor_smem;
   g->smem = smem;
-  g->counter_bytes = g->split > 1 ? kCounterBytes : 0;
-  g->partial_bytes = g->split > 1 ? (size_t)g->tiles * g->split * g->umma_n * 128 * sizeof(float) : 0;
+  const bool ws_split = g->split > 1 && !g->cluster;
+  g->counter_bytes = ws_split ? kCounterBytes : 0;
+  g->partial_bytes = ws_split ? (size_t)g->tiles * g->split * g->umma_n * 128 * sizeof(float) : 0;
   return FP8MM_OK;
 }
 
@@ -194,7 +201,7 @@ int make_output_map(void* c, int m, int n, long long ldc, CUtensorMap* out) {
 // ----------------------------------------------------------------- launch
 struct DeviceInfo {
   int sms = 0;
-  bool attr_set[32] = {};
+  bool attr_set[40] = {};
 };
 DeviceInfo g_dev[kMaxDevices];
 
@@ -218,7 +225,7 @@ bool use_pdl() {
   return v;
 }
 
-template <int UMMA_N, bool SWAP, bool SPLITK>
+template <int UMMA_N, bool SWAP, int SPLITK>
 int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
                const OutTargets& outs, const KParams& p, int grid, cudaStream_t stream) {
   auto kern = fp8mm_umma_kernel<UMMA_N, SWAP, SPLITK>;
@@ -236,11 +243,22 @@ int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, 
   lc.blockDim = dim3(g.threads);
   lc.dynamicSmemBytes = g.smem;
   lc.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (use_pdl()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (SPLITK == 2) {                       // the split CTAs of a tile form one cluster
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = g.split;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   lc.attrs = attr;
-  lc.numAttrs = use_pdl() ? 1 : 0;
+  lc.numAttrs = na;
   const cudaError_t e = cudaLaunchKernelEx(&lc, kern, tm_tok, tm_wgt, outs, p);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return e == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
@@ -251,11 +269,11 @@ int launch_pair(int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUt
   auto kern = fp8mm_umma_2cta_kernel;
   {
     std::lock_guard<std::mutex> lk(g_mu);
-    if (!g_dev[dev].attr_set[31]) {
+    if (!g_dev[dev].attr_set[39]) {
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem) !=
           cudaSuccess)
         return FP8MM_E_LAUNCH;
-      g_dev[dev].attr_set[31] = true;
+      g_dev[dev].attr_set[39] = true;
     }
   }
   cudaLaunchConfig_t lc = {};
@@ -263,22 +281,39 @@ int launch_pair(int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUt
   lc.blockDim = dim3(g.threads);
   lc.dynamicSmemBytes = g.smem;
   lc.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (use_pdl()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
   lc.attrs = attr;
-  lc.numAttrs = use_pdl() ? 1 : 0;
+  lc.numAttrs = na;
   const cudaError_t e = cudaLaunchKernelEx(&lc, kern, tm_tok, tm_wgt, outs, p);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return e == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
 }
 
+// Split-K through a cluster (distributed shared memory) when the split is 2, 4 or 8, else
+// through the workspace.  FP8MM_SPLIT_MODE=workspace forces the workspace path.
+bool cluster_split_allowed() {
+  static const bool v = []() {
+    const char* e = getenv("FP8MM_SPLIT_MODE");
+    return !(e != nullptr && e[0] == 'w');
+  }();
+  return v;
+}
+
 template <int UMMA_N, bool SWAP>
 int launch(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
            const OutTargets& outs, const KParams& p, int grid, cudaStream_t stream) {
-  if (g.split > 1)
-    return launch_one<UMMA_N, SWAP, true>(2 * slot + 1, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
-  return launch_one<UMMA_N, SWAP, false>(2 * slot, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+  if (g.split > 1) {
+    if (g.cluster)
+      return launch_one<UMMA_N, SWAP, 2>(3 * slot + 2, dev, g, tm_tok, tm_wgt, outs, p, p.num_units, stream);
+    return launch_one<UMMA_N, SWAP, 1>(3 * slot + 1, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+  }
+  return launch_one<UMMA_N, SWAP, 0>(3 * slot, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
 }
 
 }  // namespace
@@ -357,7 +392,7 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
       (reinterpret_cast<uintptr_t>(a->C) & 15) || a->ldc < a->N || (a->ldc % 8) != 0)
     return FP8MM_E_ALIGN;
   const size_t need = kStatusBytes + g.counter_bytes + g.partial_bytes;
-  if (g.split > 1 && (workspace == nullptr || ws_bytes < need)) return FP8MM_E_WORKSPACE;
+  if (g.split > 1 && !g.cluster && (workspace == nullptr || ws_bytes < need)) return FP8MM_E_WORKSPACE;
   if (workspace != nullptr && ws_bytes < kStatusBytes) return FP8MM_E_WORKSPACE;
 
   int dev = 0;
@@ -395,8 +430,8 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
   p.Bs = a->Bs;
   p.C = static_cast<__nv_bfloat16*>(a->C);
   p.status = reinterpret_cast<int*>(ws);
-  p.ws_counter = g.split > 1 ? reinterpret_cast<int*>(ws + kStatusBytes) : nullptr;
-  p.ws_partial = g.split > 1 ? reinterpret_cast<float*>(ws + kStatusBytes + g.counter_bytes) : nullptr;
+  p.ws_counter = (g.split > 1 && !g.cluster) ? reinterpret_cast<int*>(ws + kStatusBytes) : nullptr;
+  p.ws_partial = (g.split > 1 && !g.cluster) ? reinterpret_cast<float*>(ws + kStatusBytes + g.counter_bytes) : nullptr;
   p.as_sm = a->as_stride_m;
   p.as_sk = a->as_stride_k;
   p.bs_sn = a->bs_stride_n;

@@ -158,7 +158,10 @@ struct KernelTraits {
   static_assert(SWAP || UMMA_N >= 128, "token-major tiles carry 128 or 256 weight rows");
 };
 
-template <int UMMA_N, bool SWAP, bool SPLITK>
+// SPLITK: 0 = one CTA owns the whole K range; 1 = fp32 partials through the global workspace;
+// 2 = the `split` CTAs of a tile form a thread-block cluster and reduce through distributed
+//     shared memory (no workspace, no counters).
+template <int UMMA_N, bool SWAP, int SPLITK>
 __global__ void __launch_bounds__(KernelTraits<UMMA_N, SWAP>::THREADS, 1)
 fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
                   const __grid_constant__ CUtensorMap tm_wgt,
@@ -382,41 +385,66 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         if (++pstage == stages) pstage = 0;
         ptx::tc_fence_after();
         const uint32_t taddr = lane_base + buf * UMMA_N;
+#define FP8MM_PROMOTE_CHUNK(dd_, ch_)                                                              \
+  do {                                                                                             \
+    if (SWAP) {                                                                                    \
+      _Pragma("unroll") for (int i_ = 0; i_ < CH; i_ += 4) {                                       \
+        const float4 s4_ = sv[((ch_) * CH + i_) >> 2];                                             \
+        acc[(ch_) * CH + i_ + 0] = fmaf(__uint_as_float(dd_[i_ + 0]), s4_.x, acc[(ch_) * CH + i_ + 0]); \
+        acc[(ch_) * CH + i_ + 1] = fmaf(__uint_as_float(dd_[i_ + 1]), s4_.y, acc[(ch_) * CH + i_ + 1]); \
+        acc[(ch_) * CH + i_ + 2] = fmaf(__uint_as_float(dd_[i_ + 2]), s4_.z, acc[(ch_) * CH + i_ + 2]); \
+        acc[(ch_) * CH + i_ + 3] = fmaf(__uint_as_float(dd_[i_ + 3]), s4_.w, acc[(ch_) * CH + i_ + 3]); \
+      }                                                                                            \
+    } else {                                                                                       \
+      _Pragma("unroll") for (int i_ = 0; i_ < CH; ++i_)                                            \
+        acc[(ch_) * CH + i_] = fmaf(__uint_as_float(dd_[i_]), sc, acc[(ch_) * CH + i_]);           \
+    }                                                                                              \
+  } while (0)
         uint32_t d[2][CH];
-        ptx::tmem_ld<CH>(taddr, d[0]);
-#pragma unroll
-        for (int ch = 0; ch < NCH; ++ch) {
+        if constexpr (NCH <= 2) {
+          // up to 64 columns per thread: every load in flight at once, one wait, then release
+          // the buffer before any FMA
+          ptx::tmem_ld<CH>(taddr, d[0]);
+          if constexpr (NCH == 2) ptx::tmem_ld<CH>(taddr + CH, d[1]);
           ptx::tmem_wait_ld();
-          if (ch + 1 < NCH) {
-            ptx::tmem_ld<CH>(taddr + (ch + 1) * CH, d[(ch + 1) & 1]);
-          } else {
-            // every tcgen05.ld of this warp has completed: hand the buffer back before the
-            // last FMAs so the next MMA into it can be issued as early as possible
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * tb_idx);
-          }
-          if (SWAP) {
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * tb_idx);
+          FP8MM_PROMOTE_CHUNK(d[0], 0);
+          if constexpr (NCH == 2) FP8MM_PROMOTE_CHUNK(d[1], 1);
+        } else {
+          ptx::tmem_ld<CH>(taddr, d[0]);
 #pragma unroll
-            for (int i = 0; i < CH; i += 4) {
-              const float4 s4 = sv[(ch * CH + i) >> 2];
-              acc[ch * CH + i + 0] = fmaf(__uint_as_float(d[ch & 1][i + 0]), s4.x, acc[ch * CH + i + 0]);
-              acc[ch * CH + i + 1] = fmaf(__uint_as_float(d[ch & 1][i + 1]), s4.y, acc[ch * CH + i + 1]);
-              acc[ch * CH + i + 2] = fmaf(__uint_as_float(d[ch & 1][i + 2]), s4.z, acc[ch * CH + i + 2]);
-              acc[ch * CH + i + 3] = fmaf(__uint_as_float(d[ch & 1][i + 3]), s4.w, acc[ch * CH + i + 3]);
+          for (int ch = 0; ch < NCH; ++ch) {
+            ptx::tmem_wait_ld();
+            if (ch + 1 < NCH) {
+              ptx::tmem_ld<CH>(taddr + (ch + 1) * CH, d[(ch + 1) & 1]);
+            } else {
+              // every tcgen05.ld of this warp has completed: hand the buffer back before the
+              // last FMAs so the next MMA into it can be issued as early as possible
+              ptx::tc_fence_before();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * tb_idx);
             }
-          } else {
-#pragma unroll
-            for (int i = 0; i < CH; ++i)
-              acc[ch * CH + i] = fmaf(__uint_as_float(d[ch & 1][i]), sc, acc[ch * CH + i]);
+            FP8MM_PROMOTE_CHUNK(d[ch & 1], ch);
           }
         }
+#undef FP8MM_PROMOTE_CHUNK
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_scempty + 8 * t);
 
       // ------------------------------------------------------------- epilogue
-      if constexpr (SPLITK) {
+      if constexpr (SPLITK == 2) {
+        // Cluster split-K: park the fp32 partial in this CTA's own shared memory (the operand ring
+        // is idle: this CTA's only unit is finished); the reduction follows the cluster barrier.
+        if (ok) {
+          float* red = reinterpret_cast<float*>(smem) + (size_t)(half * CPT) * 128 + row;
+#pragma unroll
+          for (int j = 0; j < CPT; ++j) red[j * 128] = acc[j];
+        }
+        break;
+      } else if constexpr (SPLITK == 1) {
         // Split-K: park the fp32 partial; the CTA that arrives last on the tile's counter
         // sums all partials in split order (bit-stable) and writes the tile.
         const size_t tile_floats = (size_t)UMMA_N * 128;
@@ -535,6 +563,60 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     }
     if (!SWAP && lane == 0) ptx::bulk_wait_all();   // stores (also those to peer GPUs) are done
     __syncwarp();
+  }
+
+  if constexpr (SPLITK == 2) {
+    // ------------------------------------------------- cluster split-K reduction
+    // Rank r of the cluster reduces, for every row, the r-th slice of each column half over all
+    // ranks in rank order (the same order as the workspace path: bit-identical results) and
+    // writes those columns of the output.
+    __syncthreads();
+    ptx::cluster_sync_all();             // every CTA's partial tile is in its shared memory
+    if (warp >= 4 && blockIdx.x < p.num_units) {
+      const UnitCoord c = decode_unit(blockIdx.x, p);
+      const int pw = warp - 4, q = warp & 3, half = pw >> 2, row = q * 32 + lane;
+      const int cps = CPT / p.split;     // columns of this half that this rank reduces
+      const int j0 = half * CPT + (int)ptx::cluster_ctarank() * cps;
+      const uint32_t red0 = ring + ((uint32_t)j0 * 128u + (uint32_t)row) * 4u;
+      if (SWAP) {
+        const int n = c.wi * 128 + row;
+        for (int jj = 0; jj < cps; ++jj) {
+          float v = 0.f;
+          for (int s = 0; s < p.split; ++s) {
+            const float x = ptx::ld_cluster_f32(ptx::map_to_cta(red0 + jj * 512, s));
+            v = s == 0 ? x : v + x;
+          }
+          const int m = c.ti * TT + j0 + jj;
+          if (m < p.M)
+            for (int d = 0; d < outs.n; ++d) outs.ptr[d][(long long)m * p.ldc + n] = __float2bfloat16_rn(v);
+        }
+      } else {
+        const int m = c.ti * 128 + row;
+        for (int jj = 0; jj < cps; jj += 8) {
+          float v[8];
+          for (int s = 0; s < p.split; ++s) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float x = ptx::ld_cluster_f32(ptx::map_to_cta(red0 + (jj + i) * 512, s));
+              v[i] = s == 0 ? x : v[i] + x;
+            }
+          }
+          const int n = c.wi * WT + j0 + jj;
+          if (m < p.M && n < p.N) {
+            __nv_bfloat162 b0 = __floats2bfloat162_rn(v[0], v[1]), b1 = __floats2bfloat162_rn(v[2], v[3]);
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(v[4], v[5]), b3 = __floats2bfloat162_rn(v[6], v[7]);
+            uint4 o;
+            o.x = *reinterpret_cast<uint32_t*>(&b0);
+            o.y = *reinterpret_cast<uint32_t*>(&b1);
+            o.z = *reinterpret_cast<uint32_t*>(&b2);
+            o.w = *reinterpret_cast<uint32_t*>(&b3);
+            for (int d = 0; d < outs.n; ++d)
+              *reinterpret_cast<uint4*>(outs.ptr[d] + (long long)m * p.ldc + n) = o;
+          }
+        }
+      }
+    }
+    ptx::cluster_sync_all();             // no rank reads this CTA's shared memory any more
   }
 
   // ---------------------------------------------------------------- teardown

@@ -43,6 +43,10 @@ extern "C" {
 #define FP8MM_IMPL_UMMA_SWAP   1    /* swap-AB: weights on the 128 UMMA rows, tokens on UMMA-N   */
 #define FP8MM_IMPL_UMMA_2CTA   2    /* CTA pairs (cta_group::2): 256 tokens x 256 weights per pair */
 
+/* cfg.flags: reduce split-K partials through the global workspace even where the cluster
+ * (distributed shared memory) reduction is available (splits of 2, 4 and 8). */
+#define FP8MM_FLAG_WORKSPACE_SPLIT 1
+
 /*
  * Operands.  Strides are in ELEMENTS and are exactly the values the reference
  * hands to its kernels (kernel_v2.py:371-372: As.stride(0), As.stride(1),
@@ -77,6 +81,10 @@ typedef struct fp8mm_args {
  *             legalised to 1, as the reference wrapper does (kernel_v2.py:355-356)
  *   group_m   token tiles per raster group (GROUP_SIZE_M), >=1
  *   max_ctas  0 = one wave sized from the SM count; otherwise an upper bound on the grid
+ * Split-K partials are reduced in split order, either by the CTA that arrives last on a
+ * per-tile counter (workspace path, kernel_v2.py:274-289) or, for splits of 2, 4 and 8, by the
+ * `split` CTAs of the tile themselves, launched as one thread-block cluster and reading each
+ * other's shared memory (no workspace traffic); both give the same bits.
  */
 typedef struct fp8mm_cfg {
   int32_t impl;
@@ -86,7 +94,7 @@ typedef struct fp8mm_cfg {
   int32_t split;
   int32_t group_m;
   int32_t max_ctas;
-  int32_t flags;      /* reserved, must be 0 */
+  int32_t flags;      /* 0, or FP8MM_FLAG_* bits */
 } fp8mm_cfg;
 
 /* Legality of (M,N,K,cfg) without touching the GPU.  Replaces the per-wrapper

@@ -29,8 +29,8 @@ def _args(A, B, As, Bs, out):
 
 
 CASES = [
-    (37, 512, 3072, "umma_swap", dict(BLOCK_T=64, SPLIT=4)),      # split-K: counters + partials in the scratch
-    (200, 3072, 2048, "umma", dict(BLOCK_W=128, SPLIT=2)),        # split-K, token-major tiles
+    (37, 512, 3072, "umma_swap", dict(BLOCK_T=64, SPLIT=3)),      # split-K: counters + partials in the scratch
+    (200, 3072, 2048, "umma", dict(BLOCK_W=128, SPLIT=2, SPLIT_VIA_WORKSPACE=True)),   # token-major tiles
     (300, 1024, 2048, "umma", dict(BLOCK_W=256, SPLIT=1)),        # unsplit: status word only
 ]
 
@@ -58,7 +58,7 @@ def test_static_scratch_matches_regular_entry_point_twice(m, n, k, impl, conf):
 def test_static_scratch_refuses_what_does_not_fit():
     lib = _lib.load()
     m, n, k = 256, 12288, 2048
-    conf = dict(BLOCK_T=256, SPLIT=4)                               # 96 tiles x 4 x 256 x 128 fp32 = 50 MB
+    conf = dict(BLOCK_T=256, SPLIT=4, SPLIT_VIA_WORKSPACE=True)     # 96 tiles x 4 x 256 x 128 fp32 = 50 MB
     cfg = engine.make_cfg("umma_swap", conf)
     assert lib.fp8mm_b200_workspace_bytes(m, n, k, ctypes.byref(cfg)) > lib.fp8mm_b200_static_scratch_bytes()
     A, B, As, Bs = (t.cuda() for t in testing.make_problem(m, n, k, seed=1))
