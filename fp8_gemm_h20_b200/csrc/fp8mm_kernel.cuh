@@ -242,36 +242,23 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   if constexpr (CPT == 128) ptx::setmaxnreg_dec<64>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    // One thread pays ~500 cycles of latency per cp.async.bulk.tensor it issues (measured), so a
-    // single issuing lane caps the ring at two loads per ~1000 cycles.  Eight lanes share the
-    // work: lane 2i issues the row-operand load and lane 2i+1 the column-operand load of every
-    // fourth K block (i = block index mod 4); their latencies overlap.
-    constexpr int kIssueLanes = 4;
-    if (lane < 2 * kIssueLanes) {
-      const int il = lane >> 1, op = lane & 1;
+    if (lane == 0) {
       const CUtensorMap* row_map = SWAP ? &tm_wgt : &tm_tok;
       const CUtensorMap* col_map = SWAP ? &tm_tok : &tm_wgt;
       int stage = 0;
-      uint32_t ph = 0, it = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
         const UnitCoord c = decode_unit(u, p);
         const int row_y = SWAP ? c.wi * 128 : c.ti * 128;
         const int col_y = SWAP ? c.ti * UMMA_N : c.wi * UMMA_N;
         const int kb0 = c.s * kbn;
-        for (int kb = 0; kb < kbn; ++kb, ++it) {
-          if ((int)(it % kIssueLanes) == il) {
-            if (!bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
-            const uint32_t dst = ring + stage * STAGE_BYTES;
-            if (op == 0) {
-              // the bytes of both loads are announced here; the other lane's copy may even
-              // complete first (the transaction count is signed)
-              ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
-              ptx::tma_load_2d(dst, row_map, bar_full + 8 * stage, (kb0 + kb) * 128, row_y);
-            } else {
-              ptx::tma_load_2d(dst + ROW_BYTES, col_map, bar_full + 8 * stage, (kb0 + kb) * 128, col_y);
-            }
-          }
+        for (int kb = 0; kb < kbn; ++kb) {
+          if (!bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
+          const uint32_t dst = ring + stage * STAGE_BYTES;
+          ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
+          ptx::tma_load_2d(dst, row_map, bar_full + 8 * stage, (kb0 + kb) * 128, row_y);
+          ptx::tma_load_2d(dst + ROW_BYTES, col_map, bar_full + 8 * stage, (kb0 + kb) * 128, col_y);
           if (++stage == stages) { stage = 0; ph ^= 1u; }
         }
       }
