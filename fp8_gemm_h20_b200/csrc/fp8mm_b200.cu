@@ -38,6 +38,7 @@ struct Geometry {
   int stages;
   int threads;
   size_t smem;
+  int stg_slabs;
   size_t counter_bytes, partial_bytes;
 };
 
@@ -88,10 +89,23 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   const size_t stage_bytes = g->pair ? 2 * 128 * 128 : 128 * 128 + (size_t)g->umma_n * 128;
   const size_t tab_rows = g->pair ? 128 : g->tt;    // token rows per CTA in the scale table
   const size_t tab_bytes = 2 * (size_t)g->kbn * tab_rows * sizeof(float) + 2 * (size_t)g->kbn * 2 * sizeof(float);
-  const size_t staging = g->swap ? 0 : (size_t)npw * 4096;   // bf16 output staging for TMA stores
-  const size_t fixed = 1024 + staging + tab_bytes + sizeof(SharedCtl);
+  size_t staging = g->swap ? 0 : (size_t)npw * 4096;   // bf16 output staging for TMA stores
+  size_t fixed = 1024 + staging + tab_bytes + sizeof(SharedCtl);
   if (fixed + 2 * stage_bytes > kMaxDynSmem) return FP8MM_E_CONFIG;
   int stages = c->stages > 0 ? c->stages : (g->pair ? 5 : 4);
+  if (stages > kMaxStages) stages = kMaxStages;
+  // 256-wide token-major tiles: a second staging slab per epilogue warp (both column halves
+  // staged and stored back to back) when it costs no ring stage
+  g->stg_slabs = 1;
+  if (!g->swap && !g->pair && g->umma_n == 256) {
+    const int fit1 = (int)((kMaxDynSmem - fixed) / stage_bytes);
+    const int want = stages < fit1 ? stages : fit1;
+    if (fixed + staging + (size_t)want * stage_bytes <= kMaxDynSmem) {
+      g->stg_slabs = 2;
+      fixed += staging;
+      staging *= 2;
+    }
+  }
   const int fit = (int)((kMaxDynSmem - fixed) / stage_bytes);
   if (stages > fit) stages = fit;
   if (stages > kMaxStages) stages = kMaxStages;
@@ -448,6 +462,7 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
   p.num_units = g.tiles * g.split;
   p.group_m = cfg->group_m;
   p.stages = g.stages;
+  p.stg_slabs = g.stg_slabs;
 
   // One CTA per SM unless the shared-memory footprint lets two share an SM.
   int per_sm = (int)((kMaxDynSmem + 1024) / (g.smem + 1024));

@@ -45,6 +45,7 @@ struct KParams {
   int num_units;       // t_tiles * w_tiles * split
   int group_m;
   int stages;
+  int stg_slabs;       // bf16 staging slabs (32 rows x 64 columns) per epilogue warp: 1 or 2
 };
 
 // Where the bf16 result goes: the caller's C and, for the fused all-gather of the N-sharded
@@ -182,9 +183,9 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
 
   const int kbn = p.kb_per_unit;
   const int stages = p.stages;
-  const uint32_t staging = ring + stages * STAGE_BYTES;   // 1024-byte aligned, NPW x 4 KB
+  const uint32_t staging = ring + stages * STAGE_BYTES;   // 1024-byte aligned, NPW x slabs x 4 KB
   unsigned char* staging_ptr = smem + (size_t)stages * STAGE_BYTES;
-  float* tab_a = reinterpret_cast<float*>(staging_ptr + T::STAGING_BYTES);       // [2][kbn][TT]
+  float* tab_a = reinterpret_cast<float*>(staging_ptr + T::STAGING_BYTES * p.stg_slabs);   // [2][kbn][TT]
   float* tab_b = tab_a + 2 * kbn * TT;                                             // [2][kbn][2]
   SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tab_b + 2 * kbn * 2);
 
@@ -531,12 +532,21 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         const int m0w = c.ti * 128 + q * 32;
         const int n0 = c.wi * WT + half * CPT;
         if (m0w < p.M && n0 < p.N) {
-          unsigned char* stg = staging_ptr + pw * 4096;
-          const uint32_t stg_addr = staging + pw * 4096;
+          // With two slabs per warp (256-wide tiles, when shared memory allows) both halves of the
+          // warp's 128 columns are staged back to back and lanes 0 and 1 issue one store each; the
+          // wait for the TMA unit to have read the staging memory then falls at the start of the
+          // NEXT unit's epilogue, a whole main loop later, instead of between the two slabs.
+          const int nsl = p.stg_slabs;
+          unsigned char* stg = staging_ptr + pw * 4096 * nsl;
+          const uint32_t stg_addr = staging + pw * 4096 * nsl;
+          constexpr int SLABS = CPT / 64;
 #pragma unroll
-          for (int sl = 0; sl < CPT / 64; ++sl) {
-            if (lane == 0) ptx::bulk_wait_read_all();   // the previous slab has left the staging buffer
-            __syncwarp();
+          for (int sl = 0; sl < SLABS; ++sl) {
+            const int so = (nsl == 2) ? sl * 4096 : 0;
+            if (sl == 0 || nsl == 1) {
+              if (lane < 2) ptx::bulk_wait_read_all();   // earlier slabs have left the staging buffer
+              __syncwarp();
+            }
 #pragma unroll
             for (int ck = 0; ck < 8; ++ck) {
               const int j = sl * 64 + ck * 8;
@@ -549,19 +559,29 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
               o.y = *reinterpret_cast<uint32_t*>(&v1);
               o.z = *reinterpret_cast<uint32_t*>(&v2);
               o.w = *reinterpret_cast<uint32_t*>(&v3);
-              *reinterpret_cast<uint4*>(stg + lane * 128 + ((ck ^ (lane & 7)) << 4)) = o;
+              *reinterpret_cast<uint4*>(stg + so + lane * 128 + ((ck ^ (lane & 7)) << 4)) = o;
             }
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              for (int d = 0; d < outs.n; ++d) ptx::tma_store_2d(&outs.map[d], stg_addr, n0 + sl * 64, m0w);
-              ptx::bulk_commit_group();
+            if (nsl == 1) {
+              ptx::fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                for (int d = 0; d < outs.n; ++d) ptx::tma_store_2d(&outs.map[d], stg_addr, n0 + sl * 64, m0w);
+                ptx::bulk_commit_group();
+              }
+            } else if (sl == SLABS - 1) {
+              ptx::fence_proxy_async_smem();
+              __syncwarp();
+              if (lane < SLABS) {
+                for (int d = 0; d < outs.n; ++d)
+                  ptx::tma_store_2d(&outs.map[d], stg_addr + lane * 4096, n0 + lane * 64, m0w);
+                ptx::bulk_commit_group();
+              }
             }
           }
         }
       }
     }
-    if (!SWAP && lane == 0) ptx::bulk_wait_all();   // stores (also those to peer GPUs) are done
+    if (!SWAP && lane < 2) ptx::bulk_wait_all();   // stores (also those to peer GPUs) are done
     __syncwarp();
   }
 
