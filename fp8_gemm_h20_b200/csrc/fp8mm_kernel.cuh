@@ -5,9 +5,10 @@
 // One CTA owns one SM and walks a list of work units (output tile x K-split).
 // Roles, by warp:
 //   warp 0      TMA producer   – streams 128-byte-wide operand tiles into a shared-memory ring
-//   warp 1      MMA issuer     – per 128-wide K block: four tcgen05.mma (K=32 each) into one of
-//                                two TMEM accumulator buffers, fresh accumulator every block
-//   warps 2-3   scale loader   – stages the activation/weight scales of the unit in shared memory
+//   warps 1-2   MMA issuers    – per 128-wide K block: four tcgen05.mma (K=32 each) into one of
+//                                the TMEM accumulator buffers, fresh accumulator every block;
+//                                warp 1 issues the even K blocks, warp 2 the odd ones
+//   warp 3      scale loader   – stages the activation/weight scales of the unit in shared memory
 //   warps 4..   promotion      – tcgen05.ld the finished K block, acc += d * (As*Bs) in FP32
 //                                registers, release the TMEM buffer, finally write bf16 (or the
 //                                split-K partial) to global memory
@@ -131,6 +132,52 @@ __device__ __forceinline__ UnitCoord decode_unit(int u, const KParams& p) {
   return c;
 }
 
+// Stage the scales of one work unit in shared memory: ta[kb][token] = As (times the tile's weight
+// scale when SWAP), tb[kb][0..1] = the weight scales of the tile's one or two 128-row blocks
+// (token-major tiles only).  Called by NT threads (tid = 0..NT-1).  A thread owns one token
+// (column x of the table) and a stride of K blocks: no divisions, up to U independent global
+// loads in flight, conflict-free shared-memory stores.
+template <int TT, int WT, bool SWAP, int NT, int U>
+__device__ __forceinline__ void stage_scales(int tid, const UnitCoord& c, const KParams& p, int kbn,
+                                             float* ta, float* tb) {
+  constexpr int TPT = TT >= NT ? NT : TT;   // threads along the token axis
+  constexpr int KP = NT / TPT;              // threads along the K-block axis
+  const int kb0 = c.s * kbn;
+  const int t0 = c.ti * TT;
+  const float* bs_row = p.Bs + (long long)(c.wi * (WT / 128)) * p.bs_sn;
+  const int x0 = tid % TPT, kp = tid / TPT;
+  for (int x = x0; x < TT; x += TPT) {
+    const int tok = min(t0 + x, p.M - 1);
+    const float* src = p.As + (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
+    const float* bsrc = bs_row + (long long)kb0 * p.bs_sk;
+    for (int kb = kp; kb < kbn; kb += KP * U) {
+      float v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int kbu = kb + u * KP;
+        v[u] = 0.f;
+        if (kbu < kbn) {
+          v[u] = __ldg(src + (long long)kbu * p.as_sk);
+          if (SWAP) v[u] *= __ldg(bsrc + (long long)kbu * p.bs_sk);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int kbu = kb + u * KP;
+        if (kbu < kbn) ta[kbu * TT + x] = v[u];
+      }
+    }
+  }
+  if (!SWAP) {
+    const int nblk_max = p.N / 128 - 1;
+    for (int idx = tid; idx < kbn * 2; idx += NT) {
+      const int kb = idx >> 1, h = idx & 1;
+      const int nb = min(c.wi * (WT / 128) + h, nblk_max);
+      tb[idx] = __ldg(p.Bs + (long long)nb * p.bs_sn + (long long)(kb0 + kb) * p.bs_sk);
+    }
+  }
+}
+
 template <int UMMA_N, bool SWAP>
 struct KernelTraits {
   static constexpr int NPW = UMMA_N >= 128 ? 8 : 4;           // promotion warps (two column halves when 8)
@@ -209,7 +256,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       ptx::mbar_init(bar_tempty + 8 * b, NPW);
     }
     for (int b = 0; b < 2; ++b) {
-      ptx::mbar_init(bar_scfull + 8 * b, 64);
+      ptx::mbar_init(bar_scfull + 8 * b, 32);
       ptx::mbar_init(bar_scempty + 8 * b, NPW);
     }
     ctl->abort = 0;
@@ -265,14 +312,24 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
-    // -------------------------------------------------------------- MMA issuer
+  } else if (warp <= 2) {
+    // ------------------------------------------------------------- MMA issuers
+    // One thread needs ~750 cycles for the waits, the four tcgen05.mma and the commit of a K
+    // block, more than the 512 cycles the tensor core needs to run them.  So two threads issue:
+    // warp 1 takes the even K blocks (counted over the whole CTA), warp 2 the odd ones.  With an
+    // even number of TMEM buffers each thread owns half of them; a tcgen05.commit covers the
+    // MMAs of its own thread only, and K blocks are independent (fresh accumulator each).
     if (lane == 0) {
+      const uint32_t par = warp - 1;
       int stage = 0;
       uint32_t ph = 0, it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
         for (int kb = 0; kb < kbn; ++kb, ++it) {
+          if ((it & 1u) != par) {
+            if (++stage == stages) { stage = 0; ph ^= 1u; }
+            continue;
+          }
           const uint32_t buf = it % NBUF, tph = (it / NBUF) & 1u;
           if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
           const uint32_t a_addr = ring + stage * STAGE_BYTES;
@@ -301,54 +358,17 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     __syncwarp();
   } else {
     // ------------------------------------------------------------ scale loader
-    const int tid = threadIdx.x - 64;
+    // Prefetches the scale tables of the CTA's second and later units while the previous unit is
+    // being promoted.  The first unit's tables are staged by the promotion warps themselves (they
+    // have nothing else to do until the first MMAs retire, and they are 4-8x as many threads);
+    // for that unit this warp only arrives, which keeps the barrier phases in step.
+    const int tid = threadIdx.x - 96;     // warp 3
     uint32_t ui = 0;
     for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
       const UnitCoord c = decode_unit(u, p);
       const uint32_t t = ui & 1u, tph = (ui >> 1) & 1u;
       if (!bw.wait(bar_scempty + 8 * t, tph ^ 1u, kWaitLoaderEmpty)) break;
-      const int kb0 = c.s * kbn;
-      const int t0 = c.ti * TT;
-      float* ta = tab_a + t * kbn * TT;
-      float* tb = tab_b + t * kbn * 2;
-      const float* bs_row = p.Bs + (long long)(c.wi * (WT / 128)) * p.bs_sn;
-      // kbn*TT activation scales (times the tile's weight scale when SWAP).  A thread owns one
-      // token (column x of the table) and a stride of K blocks; no divisions, up to eight
-      // independent global loads in flight, conflict-free shared-memory stores.
-      constexpr int TPT = TT >= 64 ? 64 : TT;   // loader threads along the token axis
-      constexpr int KP = 64 / TPT;              // loader threads along the K-block axis
-      constexpr int U = 8;
-      const int x0 = tid % TPT, kp = tid / TPT;
-      for (int x = x0; x < TT; x += TPT) {
-        const int tok = min(t0 + x, p.M - 1);
-        const float* src = p.As + (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
-        const float* bsrc = bs_row + (long long)kb0 * p.bs_sk;
-        for (int kb = kp; kb < kbn; kb += KP * U) {
-          float v[U];
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int kbu = kb + u * KP;
-            v[u] = 0.f;
-            if (kbu < kbn) {
-              v[u] = __ldg(src + (long long)kbu * p.as_sk);
-              if (SWAP) v[u] *= __ldg(bsrc + (long long)kbu * p.bs_sk);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int kbu = kb + u * KP;
-            if (kbu < kbn) ta[kbu * TT + x] = v[u];
-          }
-        }
-      }
-      if (!SWAP) {
-        const int nblk_max = p.N / 128 - 1;
-        for (int idx = tid; idx < kbn * 2; idx += 64) {
-          const int kb = idx >> 1, h = idx & 1;
-          const int nb = min(c.wi * (WT / 128) + h, nblk_max);
-          tb[idx] = __ldg(p.Bs + (long long)nb * p.bs_sn + (long long)(kb0 + kb) * p.bs_sk);
-        }
-      }
+      if (ui > 0) stage_scales<TT, WT, SWAP, 32, 16>(tid, c, p, kbn, tab_a + t * kbn * TT, tab_b + t * kbn * 2);
       ptx::mbar_arrive(bar_scfull + 8 * t);
     }
   }
@@ -366,6 +386,11 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
       const UnitCoord c = decode_unit(u, p);
       const uint32_t t = ui & 1u, sph = (ui >> 1) & 1u;
+      if (ui == 0) {
+        // first unit of the CTA: all promotion threads stage its scales (one round of loads)
+        stage_scales<TT, WT, SWAP, NPW * 32, 8>(threadIdx.x - kProducerThreads, c, p, kbn, tab_a, tab_b);
+        ptx::bar_sync(1, NPW * 32);
+      }
       bool ok = bw.wait(bar_scfull + 8 * t, sph, kWaitPromoScale);
       const float* ta = tab_a + t * kbn * TT;
       const float* tb = tab_b + t * kbn * 2;
@@ -414,21 +439,25 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           FP8MM_PROMOTE_CHUNK(d[0], 0);
           if constexpr (NCH == 2) FP8MM_PROMOTE_CHUNK(d[1], 1);
         } else {
+          // 128 columns per thread in two waits instead of four: the chain from "MMAs done" to
+          // "buffer handed back" is two TMEM round trips plus 32 FMAs, and it is that chain (with
+          // only two 256-column buffers) that paces the kernel, not the FMA or load throughput.
+          static_assert(NCH == 4, "two pairs of 32-column loads");
           ptx::tmem_ld<CH>(taddr, d[0]);
-#pragma unroll
-          for (int ch = 0; ch < NCH; ++ch) {
-            ptx::tmem_wait_ld();
-            if (ch + 1 < NCH) {
-              ptx::tmem_ld<CH>(taddr + (ch + 1) * CH, d[(ch + 1) & 1]);
-            } else {
-              // every tcgen05.ld of this warp has completed: hand the buffer back before the
-              // last FMAs so the next MMA into it can be issued as early as possible
-              ptx::tc_fence_before();
-              __syncwarp();
-              if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * tb_idx);
-            }
-            FP8MM_PROMOTE_CHUNK(d[ch & 1], ch);
-          }
+          ptx::tmem_ld<CH>(taddr + CH, d[1]);
+          ptx::tmem_wait_ld();
+          FP8MM_PROMOTE_CHUNK(d[0], 0);
+          ptx::tmem_ld<CH>(taddr + 2 * CH, d[0]);
+          FP8MM_PROMOTE_CHUNK(d[1], 1);
+          ptx::tmem_ld<CH>(taddr + 3 * CH, d[1]);
+          ptx::tmem_wait_ld();
+          // every tcgen05.ld of this warp has completed: hand the buffer back before the last
+          // FMAs so the next MMA into it can be issued as early as possible
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * tb_idx);
+          FP8MM_PROMOTE_CHUNK(d[0], 2);
+          FP8MM_PROMOTE_CHUNK(d[1], 3);
         }
 #undef FP8MM_PROMOTE_CHUNK
       }
