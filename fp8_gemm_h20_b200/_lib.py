@@ -29,6 +29,7 @@ SYMBOLS = (
     "fp8mm_b200_gemm_bcast",
     "fp8mm_b200_gemm_static_scratch",
     "fp8mm_b200_quantize_act",
+    "fp8mm_b200_expand_ue8m0",
     "fp8mm_b200_static_scratch_bytes",
     "fp8mm_b200_last_status",
     "fp8mm_b200_strerror",
@@ -97,6 +98,9 @@ def load():
                                                 ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                                 ctypes.c_float, ctypes.c_void_p]
         lib.fp8mm_b200_quantize_act.restype = ctypes.c_int
+        lib.fp8mm_b200_expand_ue8m0.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
+                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p]
+        lib.fp8mm_b200_expand_ue8m0.restype = ctypes.c_int
         lib.fp8mm_b200_static_scratch_bytes.argtypes = []
         lib.fp8mm_b200_static_scratch_bytes.restype = ctypes.c_size_t
         lib.fp8mm_b200_last_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]

@@ -89,3 +89,42 @@ extern "C" int fp8mm_b200_quantize_act(const void* x_bf16, void* a_e4m3, float* 
       as_stride_k, floor_);
   return cudaGetLastError() == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
 }
+
+// ------------------------------------------------------------------ UE8M0 scale expansion
+// UE8M0 is the 8-bit exponent-only scale format of Blackwell block-scaled MMA and of DeepGEMM's
+// sm_100 path: value = 2^(e - 127).  SGLang on Blackwell re-quantises block-FP8 weight scales to
+// it and packs four consecutive K-block exponents into one int32, MN-major.  The GEMM of this
+// library takes FP32 scales, so the packed form is expanded once per weight (exact: a power of two
+// is an FP32 bit pattern).  e = 0 gives the subnormal 2^-127, e = 255 (NaN in the format) gives a
+// quiet NaN.
+__global__ void expand_ue8m0_kernel(const uint8_t* __restrict__ src, float* __restrict__ dst, int rows,
+                                    int kblocks, long long row_stride, long long col_stride, int packed4) {
+  const long long total = (long long)rows * kblocks;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / kblocks), kb = (int)(i - (long long)r * kblocks);
+    uint32_t e;
+    if (packed4) {
+      // strides count int32 words; byte kb%4 of the word (little endian) is K block kb
+      const long long w = (long long)r * row_stride + (long long)(kb >> 2) * col_stride;
+      e = src[w * 4 + (kb & 3)];
+    } else {
+      e = src[(long long)r * row_stride + (long long)kb * col_stride];
+    }
+    const uint32_t bits = e == 0u ? 0x00400000u : (e == 255u ? 0x7FC00000u : (e << 23));
+    dst[i] = __uint_as_float(bits);
+  }
+}
+
+extern "C" int fp8mm_b200_expand_ue8m0(const void* src, float* dst, int32_t rows, int32_t kblocks,
+                                       int64_t row_stride, int64_t col_stride, int32_t packed4, void* stream) {
+  if (src == nullptr || dst == nullptr) return FP8MM_E_NULL;
+  if (rows < 1 || kblocks < 1) return FP8MM_E_SHAPE;
+  if (packed4 != 0 && (reinterpret_cast<uintptr_t>(src) & 3)) return FP8MM_E_ALIGN;
+  const long long total = (long long)rows * kblocks;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  expand_ue8m0_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(src), dst, rows, kblocks, row_stride, col_stride, packed4);
+  return cudaGetLastError() == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
+}

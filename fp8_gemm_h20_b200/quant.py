@@ -24,3 +24,30 @@ def quantize_activations(x, floor=1e-10):
     if rc != 0:
         raise RuntimeError(f"fp8mm_b200_quantize_act failed: {_lib.strerror(rc)}")
     return A, As
+
+
+def expand_ue8m0(scales):
+    """UE8M0 scales -> float32 [rows, kblocks] (contiguous), exactly: value = 2^(e - 127).
+
+    `scales` is a CUDA tensor of either uint8 [rows, kblocks] (any strides), or int32
+    [rows, ceil(kblocks/4)] with four consecutive K blocks per word (the packed MN-major form
+    DeepGEMM uses on sm_100; any strides) - then every byte of every word is expanded, i.e.
+    kblocks = 4 * words per row."""
+    import torch
+    if scales.ndim != 2 or not scales.is_cuda:
+        raise ValueError("scales must be a 2-D CUDA tensor")
+    if scales.dtype == torch.uint8:
+        rows, kblocks, packed = scales.shape[0], scales.shape[1], 0
+    elif scales.dtype == torch.int32:
+        rows, kblocks, packed = scales.shape[0], scales.shape[1] * 4, 1
+    else:
+        raise ValueError("UE8M0 scales come as uint8 exponents or as int32 words of four exponents")
+    out = torch.empty((rows, kblocks), dtype=torch.float32, device=scales.device)
+    lib = _lib.load()
+    with torch.cuda.device(scales.device):
+        rc = lib.fp8mm_b200_expand_ue8m0(scales.data_ptr(), out.data_ptr(), rows, kblocks, scales.stride(0),
+                                         scales.stride(1), packed,
+                                         torch.cuda.current_stream(scales.device).cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"fp8mm_b200_expand_ue8m0 failed: {_lib.strerror(rc)}")
+    return out

@@ -172,6 +172,17 @@ int fp8mm_b200_quantize_act(const void* x_bf16, void* a_e4m3, float* as, int32_t
                             int64_t ldx, int64_t as_stride_m, int64_t as_stride_k, float floor_,
                             void* stream);
 
+/* UE8M0 scales (8-bit exponent, value 2^(e-127): the scale format of Blackwell block-scaled MMA,
+ * which SGLang/DeepGEMM switch to on sm_100) -> contiguous fp32 [rows, kblocks], exactly.
+ * packed4 = 0: src is bytes, element (r, kb) at src[r*row_stride + kb*col_stride] (strides in bytes).
+ * packed4 = 1: src is int32 words holding four consecutive K blocks each (byte kb%4 of word kb/4,
+ *              little endian), word (r, kb/4) at r*row_stride + (kb/4)*col_stride (strides in words),
+ *              which covers DeepGEMM's MN-major layout (row_stride 1, col_stride = aligned rows).
+ * The reference has no such path: its adapter declines when DEEPGEMM_SCALE_UE8M0 is set
+ * (sgl_patch/fp8mm_sglang_patch.py:41), so it never engages on a stock Blackwell SGLang. */
+int fp8mm_b200_expand_ue8m0(const void* src, float* dst, int32_t rows, int32_t kblocks,
+                            int64_t row_stride, int64_t col_stride, int32_t packed4, void* stream);
+
 /* After the stream has been synchronised: 0 if no bounded device-side wait gave
  * up since the workspace was initialised, else FP8MM_E_DEVICE_TIMEOUT; *detail
  * (optional) receives the role/barrier code recorded by the kernel.  Blocking. */

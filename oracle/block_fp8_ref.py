@@ -188,3 +188,21 @@ def make_inputs(m, n, k, seed, mode="normal"):
     A, As = quantize_activations(x, 1e-6)
     B, Bs = quantize_weights(w, 1e-6)
     return A, B, As, Bs
+
+
+def expand_ue8m0(e):
+    """UE8M0 exponents (uint8 array) -> float32 2^(e-127); 255 is NaN (the format's only special
+    value).  The format is the OCP MX scale type that Blackwell's block-scaled MMA and DeepGEMM's
+    sm_100 path use; the reference's adapter only tests for it (sgl_patch/fp8mm_sglang_patch.py:41)."""
+    e = np.asarray(e, dtype=np.uint8)
+    with np.errstate(over="ignore"):
+        out = np.ldexp(np.float32(1.0), e.astype(np.int32) - 127).astype(np.float32)
+    out[e == 255] = np.float32("nan")
+    return out
+
+
+def unpack_ue8m0_words(words):
+    """int32 [rows, w] with four consecutive K-block exponents per word (little endian) ->
+    uint8 [rows, 4*w]."""
+    w = np.ascontiguousarray(np.asarray(words, dtype=np.int32))
+    return w.view(np.uint8).reshape(w.shape[0], w.shape[1] * 4)

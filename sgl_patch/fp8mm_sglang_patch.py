@@ -12,6 +12,12 @@ Environment:
   FP8MM_PROFILE=35b_tp1|122b_tp4   tuning profile (default 35b_tp1)
   FP8MM_HOME=/path/to/this/repo    prepended to sys.path
   FP8MM_DISABLE_DG_PRECOMPILE=1    also skip DeepGEMM's all-M JIT precompile, unused once patched
+  FP8MM_UE8M0=1                    also engage when SGLang runs with DEEPGEMM_SCALE_UE8M0 (its default
+                                   on Blackwell): power-of-two scales are taken as float32, or expanded
+                                   from the packed int32 form once per weight; the activation quantiser
+                                   is asked for power-of-two scales (scale_ue8m0=True).  Without this
+                                   switch such calls go to SGLang's own function, as in the reference
+                                   adapter (sgl_patch/fp8mm_sglang_patch.py:41).
 """
 import os
 import sys
@@ -38,13 +44,36 @@ if os.environ.get("FP8MM_ENABLE") == "1":
         quantize = mod.sglang_per_token_group_quant_fp8
         stats = {"ours": 0, "fallback": 0}
 
+        ue8m0_mode = os.environ.get("FP8MM_UE8M0") == "1"
+        expanded = {}     # packed weight scales -> float32, keyed by storage address (weights are static)
+
+        def weight_scales_f32(weight, weight_scale):
+            """float32 [N/128, K/128] scales of a weight whose scales are UE8M0 words (int32, four
+            K blocks per word, one row per 128-row block or per weight row)."""
+            key = (weight_scale.data_ptr(), tuple(weight_scale.shape), tuple(weight_scale.stride()))
+            hit = expanded.get(key)
+            if hit is None:
+                from fp8_gemm_h20_b200.quant import expand_ue8m0
+                n, k = weight.shape
+                full = expand_ue8m0(weight_scale)[:, :k // 128]
+                hit = (full if full.shape[0] == n // 128 else full[::128]).contiguous()
+                expanded[key] = hit
+            return hit
+
         def eligible(input, weight, block_size, weight_scale, input_scale):
             if input_scale is not None or input.dtype != torch.bfloat16:
                 return False
-            if weight_scale.dtype != torch.float32 or list(block_size) != [128, 128]:
+            if list(block_size) != [128, 128]:
                 return False
-            if getattr(mod, "DEEPGEMM_SCALE_UE8M0", False):
+            ue8m0 = bool(getattr(mod, "DEEPGEMM_SCALE_UE8M0", False))
+            if ue8m0 and not ue8m0_mode:
                 return False
+            if weight_scale.dtype != torch.float32:
+                n, k = weight.shape
+                if not (ue8m0 and weight_scale.dtype == torch.int32 and weight_scale.ndim == 2
+                        and weight_scale.shape[0] in (n // 128, n)
+                        and weight_scale.shape[1] * 4 >= k // 128):
+                    return False
             if not (input.is_contiguous() and weight.is_contiguous()):
                 return False
             if weight.dtype != torch.float8_e4m3fn:
@@ -60,8 +89,14 @@ if os.environ.get("FP8MM_ENABLE") == "1":
                 stats["ours"] += 1
                 n, k = weight.shape
                 # row-major [M, K/128] float32 activation scales, the layout matmul expects
-                q, s = quantize(input.view(-1, k), block_size[1], column_major_scales=False,
-                                scale_tma_aligned=False)
+                if getattr(mod, "DEEPGEMM_SCALE_UE8M0", False):
+                    q, s = quantize(input.view(-1, k), block_size[1], column_major_scales=False,
+                                    scale_tma_aligned=False, scale_ue8m0=True)
+                    if weight_scale.dtype != torch.float32:
+                        weight_scale = weight_scales_f32(weight, weight_scale)
+                else:
+                    q, s = quantize(input.view(-1, k), block_size[1], column_major_scales=False,
+                                    scale_tma_aligned=False)
                 out = fp8mm.matmul(q, weight, s, weight_scale, profile=profile)
                 if bias is not None:
                     out = out + bias

@@ -111,3 +111,16 @@ def test_product_torch_reference_agrees_with_oracle():
     want = oracle.gemm_fp32(A.view(torch.uint8).numpy(), B.view(torch.uint8).numpy(), As.numpy(), Bs.numpy())
     got = testing.reference_fp32(A, B, As, Bs).numpy()
     assert np.abs(got - want).max() <= 4e-6 * np.abs(want).max()
+
+
+def test_ue8m0_expansion_known_answers():
+    """UE8M0 = exponent-only scale, 2^(e-127); 127 -> 1.0, 0 -> 2^-127 (subnormal), 255 -> NaN."""
+    from oracle.block_fp8_ref import expand_ue8m0, unpack_ue8m0_words
+    e = np.array([0, 1, 120, 126, 127, 128, 134, 254], dtype=np.uint8)
+    v = expand_ue8m0(e)
+    assert v.dtype == np.float32
+    assert v.view(np.uint32).tolist() == [0x00400000] + [int(x) << 23 for x in e[1:]]
+    assert v[4] == 1.0 and v[5] == 2.0 and v[3] == 0.5 and v[2] == 2.0 ** -7
+    assert np.isnan(expand_ue8m0(np.array([255], dtype=np.uint8))[0])
+    words = np.array([[0x7F7E7D7C, 0x01000280 - (1 << 32)]], dtype=np.int64).astype(np.int32)
+    assert unpack_ue8m0_words(words).tolist() == [[0x7C, 0x7D, 0x7E, 0x7F, 0x80, 0x02, 0x00, 0x01]]
