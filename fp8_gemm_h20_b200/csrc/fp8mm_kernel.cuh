@@ -134,38 +134,35 @@ __device__ __forceinline__ UnitCoord decode_unit(int u, const KParams& p) {
 
 // Stage the scales of one work unit in shared memory: ta[kb][token] = As (times the tile's weight
 // scale when SWAP), tb[kb][0..1] = the weight scales of the tile's one or two 128-row blocks
-// (token-major tiles only).  Called by NT threads (tid = 0..NT-1).  A thread owns one token
-// (column x of the table) and a stride of K blocks: no divisions, up to U independent global
-// loads in flight, conflict-free shared-memory stores.
+// (token-major tiles only).  Called by NT threads (tid = 0..NT-1).  The table is walked as one flat
+// index (kb * TT + token, TT a power of two: no divisions), U independent global loads per thread
+// in flight at a time whatever the shape of the table, conflict-free shared-memory stores.
 template <int TT, int WT, bool SWAP, int NT, int U>
 __device__ __forceinline__ void stage_scales(int tid, const UnitCoord& c, const KParams& p, int kbn,
                                              float* ta, float* tb) {
-  constexpr int TPT = TT >= NT ? NT : TT;   // threads along the token axis
-  constexpr int KP = NT / TPT;              // threads along the K-block axis
+  static_assert((TT & (TT - 1)) == 0, "token tile must be a power of two");
   const int kb0 = c.s * kbn;
   const int t0 = c.ti * TT;
-  const float* bs_row = p.Bs + (long long)(c.wi * (WT / 128)) * p.bs_sn;
-  const int x0 = tid % TPT, kp = tid / TPT;
-  for (int x = x0; x < TT; x += TPT) {
-    const int tok = min(t0 + x, p.M - 1);
-    const float* src = p.As + (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
-    const float* bsrc = bs_row + (long long)kb0 * p.bs_sk;
-    for (int kb = kp; kb < kbn; kb += KP * U) {
-      float v[U];
+  const float* as0 = p.As + (long long)kb0 * p.as_sk;
+  const float* bs0 = p.Bs + (long long)(c.wi * (WT / 128)) * p.bs_sn + (long long)kb0 * p.bs_sk;
+  const int total = kbn * TT;
+  for (int base = tid; base < total; base += NT * U) {
+    float v[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int kbu = kb + u * KP;
-        v[u] = 0.f;
-        if (kbu < kbn) {
-          v[u] = __ldg(src + (long long)kbu * p.as_sk);
-          if (SWAP) v[u] *= __ldg(bsrc + (long long)kbu * p.bs_sk);
-        }
+    for (int u = 0; u < U; ++u) {
+      const int idx = base + u * NT;
+      v[u] = 0.f;
+      if (idx < total) {
+        const int kb = idx / TT, x = idx % TT;
+        const int tok = min(t0 + x, p.M - 1);
+        v[u] = __ldg(as0 + (long long)tok * p.as_sm + (long long)kb * p.as_sk);
+        if (SWAP) v[u] *= __ldg(bs0 + (long long)kb * p.bs_sk);
       }
+    }
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int kbu = kb + u * KP;
-        if (kbu < kbn) ta[kbu * TT + x] = v[u];
-      }
+    for (int u = 0; u < U; ++u) {
+      const int idx = base + u * NT;
+      if (idx < total) ta[idx] = v[u];
     }
   }
   if (!SWAP) {
