@@ -324,6 +324,11 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
         for (int kb = 0; kb < kbn; ++kb, ++it) {
           if ((it & 1u) != par) {
+            // The other thread's block.  Its operands are still awaited here, so that this thread
+            // sees every slot of the ring fill in order: a parity wait can only tell the current
+            // phase from the one before, and a slot whose previous fill this thread had never
+            // seen complete could otherwise read as "already full".
+            if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
             if (++stage == stages) { stage = 0; ph ^= 1u; }
             continue;
           }
