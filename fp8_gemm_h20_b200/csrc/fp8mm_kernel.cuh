@@ -193,11 +193,6 @@ struct KernelTraits {
   // 128- and 64-column tiles get four, narrower ones eight.
   static constexpr int NBUF = UMMA_N == 256 ? 2 : (UMMA_N >= 64 ? 4 : 8);
   static constexpr uint32_t TMEM_COLS = NBUF * UMMA_N < 32 ? 32 : NBUF * UMMA_N;
-  // A K-block partial can be produced and consumed as independent column halves (own MMAs,
-  // own barriers).  Measured slower: every tcgen05.commit costs the issuing thread ~250
-  // cycles, and halves double the commits.  Kept at 1.
-  static constexpr int HALVES = 1;
-  static constexpr int NH = UMMA_N / HALVES;                  // N of one tcgen05.mma
   // bf16 output staging for TMA stores (token-major tiles): 32 rows x 64 columns per warp
   static constexpr uint32_t STAGING_BYTES = SWAP ? 0u : NPW * 4096u;
   static_assert(SWAP || UMMA_N >= 128, "token-major tiles carry 128 or 256 weight rows");
@@ -214,9 +209,8 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   using T = KernelTraits<UMMA_N, SWAP>;
   constexpr int NPW = T::NPW, CPT = T::CPT, CH = T::CH, NCH = T::NCH, TT = T::TT, WT = T::WT;
   constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES, ROW_BYTES = T::ROW_BYTES;
-  constexpr int HALVES = T::HALVES, NH = T::NH, NBUF = T::NBUF;
-  static_assert(HALVES == 1, "one barrier pair per TMEM buffer");
-  constexpr uint32_t IDESC = ptx::idesc_f8_m128(NH);
+  constexpr int NBUF = T::NBUF;
+  constexpr uint32_t IDESC = ptx::idesc_f8_m128(UMMA_N);
 
   extern __shared__ unsigned char smem_raw[];
   // Operand tiles need 1024-byte alignment for the 128-byte swizzle.
@@ -336,21 +330,16 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
           const uint32_t a_addr = ring + stage * STAGE_BYTES;
           const uint64_t a_desc = ptx::smem_desc_k128(a_addr);
+          if (!bw.wait(bar_tempty + 8 * buf, tph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint64_t b_desc = ptx::smem_desc_k128(a_addr + ROW_BYTES);
+          const uint32_t d_tmem = tmem_base + buf * UMMA_N;
 #pragma unroll
-          for (uint32_t h = 0; h < (uint32_t)HALVES; ++h) {
-            const uint32_t tb_idx = buf;
-            if (!bw.wait(bar_tempty + 8 * tb_idx, tph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
-            ptx::tc_fence_after();
-            const uint64_t b_desc = ptx::smem_desc_k128(a_addr + ROW_BYTES + h * NH * 128);
-            const uint32_t d_tmem = tmem_base + buf * UMMA_N + h * NH;
-#pragma unroll
-            for (uint32_t k = 0; k < 4; ++k) {
-              // 32 fp8 = 32 bytes along K inside the swizzle span: +2 in 16-byte address units.
-              ptx::umma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, k);
-            }
-            ptx::umma_commit(bar_tfull + 8 * tb_idx);  // this half's K-block partial is ready
+          for (uint32_t k = 0; k < 4; ++k) {
+            // 32 fp8 = 32 bytes along K inside the swizzle span: +2 in 16-byte address units.
+            ptx::umma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, k);
           }
-          if (!ok) break;
+          ptx::umma_commit(bar_tfull + 8 * buf);   // this K block's partial product is ready
           // No second commit for the ring slot: a tcgen05.commit costs this thread ~250 cycles.
           // The promotion warps see the same completion (tfull) and release the slot.
           if (++stage == stages) { stage = 0; ph ^= 1u; }
