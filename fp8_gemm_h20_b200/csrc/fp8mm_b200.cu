@@ -39,6 +39,7 @@ struct Geometry {
   int threads;
   size_t smem;
   int stg_slabs;
+  int kg;              // K blocks per ring slot (1 or 2)
   size_t counter_bytes, partial_bytes;
 };
 
@@ -48,7 +49,7 @@ bool cluster_split_allowed();
 int check_cfg(int M, int N, int K, const fp8mm_cfg* c) {
   if (c == nullptr) return FP8MM_E_NULL;
   if (M < 1 || N < 128 || K < 128 || (N % 128) != 0 || (K % 128) != 0) return FP8MM_E_SHAPE;
-  if ((c->flags & ~FP8MM_FLAG_WORKSPACE_SPLIT) != 0) return FP8MM_E_CONFIG;
+  if ((c->flags & ~(FP8MM_FLAG_WORKSPACE_SPLIT | FP8MM_FLAG_K_PAIRS)) != 0) return FP8MM_E_CONFIG;
   if (c->split < 1 || c->group_m < 1 || c->stages < 0 || c->max_ctas < 0) return FP8MM_E_CONFIG;
   if (c->impl == FP8MM_IMPL_UMMA) {
     if (c->block_t != 128) return FP8MM_E_CONFIG;
@@ -86,7 +87,9 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
                !(c->flags & FP8MM_FLAG_WORKSPACE_SPLIT);
   const int npw = g->umma_n >= 128 ? 8 : 4;
   g->threads = kProducerThreads + npw * 32;
-  const size_t stage_bytes = g->pair ? 2 * 128 * 128 : 128 * 128 + (size_t)g->umma_n * 128;
+  // two K blocks per ring slot: narrow swap-AB tiles only, and only if every split has an even count
+  g->kg = ((c->flags & FP8MM_FLAG_K_PAIRS) && g->swap && g->umma_n <= 64 && g->kbn % 2 == 0) ? 2 : 1;
+  const size_t stage_bytes = g->pair ? 2 * 128 * 128 : g->kg * (128 * 128 + (size_t)g->umma_n * 128);
   const size_t tab_rows = g->pair ? 128 : g->tt;    // token rows per CTA in the scale table
   const size_t tab_bytes = 2 * (size_t)g->kbn * tab_rows * sizeof(float) + 2 * (size_t)g->kbn * 2 * sizeof(float);
   size_t staging = g->swap ? 0 : (size_t)npw * 4096;   // bf16 output staging for TMA stores
@@ -147,7 +150,7 @@ EncodeTiledFn encode_fn() {
 
 struct MapKey {
   const void* ptr;
-  int rows, k, box_rows;
+  int rows, k, box_rows;     // box_rows carries the K blocks per box in its upper bits
   bool operator==(const MapKey& o) const {
     return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows;
   }
@@ -167,8 +170,10 @@ std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 
 // Row-major [rows, k] bytes, box = box_rows x 128 bytes, 128-byte swizzle, zero fill
 // outside the tensor.  The encoding depends only on (pointer, shape, box): cached.
-int get_tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* out) {
-  const MapKey key{ptr, rows, k, box_rows};
+// kg = 2: the same bytes seen as a 3-D tensor (128 bytes, rows, K blocks) with a box of two K
+// blocks, so that one copy delivers two consecutive operand tiles.
+int get_tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* out, int kg = 1) {
+  const MapKey key{ptr, rows, k, box_rows | (kg << 16)};
   {
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_maps.find(key);
@@ -184,9 +189,20 @@ int get_tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* 
   cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1u, 1u};
   CUtensorMap m;
-  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides,
-                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r;
+  if (kg == 1) {
+    r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides,
+           box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    cuuint64_t dims3[3] = {128u, (cuuint64_t)rows, (cuuint64_t)(k / 128)};
+    cuuint64_t strides3[2] = {(cuuint64_t)k, 128u};          // bytes: next row, next K block
+    cuuint32_t box3[3] = {128u, (cuuint32_t)box_rows, (cuuint32_t)kg};
+    cuuint32_t estr3[3] = {1u, 1u, 1u};
+    r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims3, strides3,
+           box3, estr3, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) return FP8MM_E_DRIVER;
   {
     std::lock_guard<std::mutex> lk(g_mu);
@@ -239,10 +255,10 @@ bool use_pdl() {
   return v;
 }
 
-template <int UMMA_N, bool SWAP, int SPLITK>
+template <int UMMA_N, bool SWAP, int SPLITK, int KG = 1>
 int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
                const OutTargets& outs, const KParams& p, int grid, cudaStream_t stream) {
-  auto kern = fp8mm_umma_kernel<UMMA_N, SWAP, SPLITK>;
+  auto kern = fp8mm_umma_kernel<UMMA_N, SWAP, SPLITK, KG>;
   {
     std::lock_guard<std::mutex> lk(g_mu);
     if (!g_dev[dev].attr_set[slot]) {
@@ -322,6 +338,17 @@ bool cluster_split_allowed() {
 template <int UMMA_N, bool SWAP>
 int launch(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
            const OutTargets& outs, const KParams& p, int grid, cudaStream_t stream) {
+  if constexpr (SWAP && UMMA_N <= 64) {
+    if (g.kg == 2) {          // slots 21..29: the two-K-blocks-per-slot variants of the narrow tiles
+      const int s2 = 21 + 3 * slot;
+      if (g.split > 1) {
+        if (g.cluster)
+          return launch_one<UMMA_N, SWAP, 2, 2>(s2 + 2, dev, g, tm_tok, tm_wgt, outs, p, p.num_units, stream);
+        return launch_one<UMMA_N, SWAP, 1, 2>(s2 + 1, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+      }
+      return launch_one<UMMA_N, SWAP, 0, 2>(s2, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+    }
+  }
   if (g.split > 1) {
     if (g.cluster)
       return launch_one<UMMA_N, SWAP, 2>(3 * slot + 2, dev, g, tm_tok, tm_wgt, outs, p, p.num_units, stream);
@@ -419,9 +446,9 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
   }
 
   CUtensorMap tm_tok, tm_wgt;
-  rc = get_tensor_map(a->A, a->M, a->K, g.swap ? g.umma_n : 128, &tm_tok);
+  rc = get_tensor_map(a->A, a->M, a->K, g.swap ? g.umma_n : 128, &tm_tok, g.kg);
   if (rc != FP8MM_OK) return rc;
-  rc = get_tensor_map(a->B, a->N, a->K, (g.swap || g.pair) ? 128 : g.umma_n, &tm_wgt);
+  rc = get_tensor_map(a->B, a->N, a->K, (g.swap || g.pair) ? 128 : g.umma_n, &tm_wgt, g.kg);
   if (rc != FP8MM_OK) return rc;
 
   OutTargets outs;

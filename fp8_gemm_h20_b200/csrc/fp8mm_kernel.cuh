@@ -201,14 +201,18 @@ struct KernelTraits {
 // SPLITK: 0 = one CTA owns the whole K range; 1 = fp32 partials through the global workspace;
 // 2 = the `split` CTAs of a tile form a thread-block cluster and reduce through distributed
 //     shared memory (no workspace, no counters).
-template <int UMMA_N, bool SWAP, int SPLITK>
+// KG = K blocks per ring slot.  With KG = 2 (small-token tiles, an even number of K blocks per
+// unit) one 3-D TMA copy per operand brings two K blocks, which halves what the producer thread
+// issues per K block; the two MMA-issuing threads then each take one block of every slot.
+template <int UMMA_N, bool SWAP, int SPLITK, int KG = 1>
 __global__ void __launch_bounds__(KernelTraits<UMMA_N, SWAP>::THREADS, 1)
 fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
                   const __grid_constant__ CUtensorMap tm_wgt,
                   const __grid_constant__ OutTargets outs, const KParams p) {
   using T = KernelTraits<UMMA_N, SWAP>;
   constexpr int NPW = T::NPW, CPT = T::CPT, CH = T::CH, NCH = T::NCH, TT = T::TT, WT = T::WT;
-  constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES, ROW_BYTES = T::ROW_BYTES;
+  constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES * KG, ROW_BYTES = T::ROW_BYTES, COL_BYTES = T::COL_BYTES;
+  static_assert(KG == 1 || KG == 2, "one or two K blocks per ring slot");
   constexpr int NBUF = T::NBUF;
   constexpr uint32_t IDESC = ptx::idesc_f8_m128(UMMA_N);
 
@@ -292,12 +296,18 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         const int row_y = SWAP ? c.wi * 128 : c.ti * 128;
         const int col_y = SWAP ? c.ti * UMMA_N : c.wi * UMMA_N;
         const int kb0 = c.s * kbn;
-        for (int kb = 0; kb < kbn; ++kb) {
+        for (int kb = 0; kb < kbn; kb += KG) {
           if (!bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
           const uint32_t dst = ring + stage * STAGE_BYTES;
           ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
-          ptx::tma_load_2d(dst, row_map, bar_full + 8 * stage, (kb0 + kb) * 128, row_y);
-          ptx::tma_load_2d(dst + ROW_BYTES, col_map, bar_full + 8 * stage, (kb0 + kb) * 128, col_y);
+          if constexpr (KG == 1) {
+            ptx::tma_load_2d(dst, row_map, bar_full + 8 * stage, (kb0 + kb) * 128, row_y);
+            ptx::tma_load_2d(dst + ROW_BYTES, col_map, bar_full + 8 * stage, (kb0 + kb) * 128, col_y);
+          } else {
+            // slot layout: [row tile kb][row tile kb+1][column tile kb][column tile kb+1]
+            ptx::tma_load_3d(dst, row_map, bar_full + 8 * stage, 0, row_y, kb0 + kb);
+            ptx::tma_load_3d(dst + KG * ROW_BYTES, col_map, bar_full + 8 * stage, 0, col_y, kb0 + kb);
+          }
           if (++stage == stages) { stage = 0; ph ^= 1u; }
         }
       }
@@ -317,22 +327,24 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       bool ok = true;
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
         for (int kb = 0; kb < kbn; ++kb, ++it) {
+          const uint32_t j = KG == 1 ? 0u : (it & 1u);   // which K block of the ring slot
           if ((it & 1u) != par) {
-            // The other thread's block.  Its operands are still awaited here, so that this thread
-            // sees every slot of the ring fill in order: a parity wait can only tell the current
-            // phase from the one before, and a slot whose previous fill this thread had never
-            // seen complete could otherwise read as "already full".
-            if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
-            if (++stage == stages) { stage = 0; ph ^= 1u; }
+            // The other thread's block.  With one K block per slot its operands are still awaited
+            // here, so that this thread sees every slot of the ring fill in order: a parity wait
+            // can only tell the current phase from the one before, and a slot whose previous fill
+            // this thread had never seen complete could otherwise read as "already full".  (With
+            // two blocks per slot each thread owns one block of every slot and waits on all.)
+            if (KG == 1 && !bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
+            if (j == KG - 1 && ++stage == stages) { stage = 0; ph ^= 1u; }
             continue;
           }
           const uint32_t buf = it % NBUF, tph = (it / NBUF) & 1u;
           if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
-          const uint32_t a_addr = ring + stage * STAGE_BYTES;
+          const uint32_t a_addr = ring + stage * STAGE_BYTES + j * ROW_BYTES;
           const uint64_t a_desc = ptx::smem_desc_k128(a_addr);
           if (!bw.wait(bar_tempty + 8 * buf, tph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
           ptx::tc_fence_after();
-          const uint64_t b_desc = ptx::smem_desc_k128(a_addr + ROW_BYTES);
+          const uint64_t b_desc = ptx::smem_desc_k128(ring + stage * STAGE_BYTES + KG * ROW_BYTES + j * COL_BYTES);
           const uint32_t d_tmem = tmem_base + buf * UMMA_N;
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k) {
@@ -342,7 +354,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           ptx::umma_commit(bar_tfull + 8 * buf);   // this K block's partial product is ready
           // No second commit for the ring slot: a tcgen05.commit costs this thread ~250 cycles.
           // The promotion warps see the same completion (tfull) and release the slot.
-          if (++stage == stages) { stage = 0; ph ^= 1u; }
+          if (j == KG - 1 && ++stage == stages) { stage = 0; ph ^= 1u; }
         }
       }
     }
@@ -397,9 +409,12 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         const float4* sv = reinterpret_cast<const float4*>(ta + kb * TT + half * CPT);
         const uint32_t tb_idx = buf;
         if (!bw.wait(bar_tfull + 8 * tb_idx, tph, kWaitPromoTmemFull)) { ok = false; break; }
-        // the MMAs of this K block have retired, so its operand tiles may be overwritten
-        if (leader) ptx::mbar_arrive(bar_empty + 8 * pstage);
-        if (++pstage == stages) pstage = 0;
+        // the MMAs of this K block (and, with two blocks per slot, of the one before: buffers are
+        // awaited in order) have retired, so the slot's operand tiles may be overwritten
+        if (KG == 1 || (it & 1u)) {
+          if (leader) ptx::mbar_arrive(bar_empty + 8 * pstage);
+          if (++pstage == stages) pstage = 0;
+        }
         ptx::tc_fence_after();
         const uint32_t taddr = lane_base + buf * UMMA_N;
 #define FP8MM_PROMOTE_CHUNK(dd_, ch_)                                                              \

@@ -34,7 +34,7 @@ def make_cfg(impl, config):
     return _lib.Cfg(impl=impl_id, block_t=int(c["BLOCK_T"]), block_w=int(c["BLOCK_W"]),
                     stages=int(c["NUM_STAGES"]), split=int(c["SPLIT"]),
                     group_m=int(c["GROUP_SIZE_M"]), max_ctas=int(c.get("MAX_CTAS", 0)),
-                    flags=1 if c.get("SPLIT_VIA_WORKSPACE") else 0)
+                    flags=(1 if c.get("SPLIT_VIA_WORKSPACE") else 0) | (2 if int(c.get("K_GROUP", 1)) == 2 else 0))
 
 
 def _workspace(torch, device, stream, nbytes):

@@ -46,6 +46,10 @@ extern "C" {
 /* cfg.flags: reduce split-K partials through the global workspace even where the cluster
  * (distributed shared memory) reduction is available (splits of 2, 4 and 8). */
 #define FP8MM_FLAG_WORKSPACE_SPLIT 1
+/* cfg.flags: two K blocks per shared-memory ring slot, fetched by one 3-D TMA copy per operand
+ * (swap-AB tiles of 16..64 tokens; needs an even number of K blocks per split, otherwise ignored).
+ * Halves the per-K-block work of the single TMA-issuing thread, which paces small-M calls. */
+#define FP8MM_FLAG_K_PAIRS 2
 
 /*
  * Operands.  Strides are in ELEMENTS and are exactly the values the reference
