@@ -579,7 +579,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           for (int sl = 0; sl < SLABS; ++sl) {
             const int so = (nsl == 2) ? sl * 4096 : 0;
             if (sl == 0 || nsl == 1) {
-              if (lane < 2) ptx::bulk_wait_read_all();   // earlier slabs have left the staging buffer
+              if (lane < 2 * kMaxOutTargets) ptx::bulk_wait_read_all();   // earlier slabs have left the staging buffer
               __syncwarp();
             }
 #pragma unroll
@@ -596,19 +596,22 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
               o.w = *reinterpret_cast<uint32_t*>(&v3);
               *reinterpret_cast<uint4*>(stg + so + lane * 128 + ((ck ^ (lane & 7)) << 4)) = o;
             }
+            // One issuing lane per (target, slab): a thread pays a few hundred cycles per TMA
+            // instruction, and with up to eight targets (fused all-gather) a single lane would
+            // spend longer issuing the stores than the tile took to compute.
             if (nsl == 1) {
               ptx::fence_proxy_async_smem();
               __syncwarp();
-              if (lane == 0) {
-                for (int d = 0; d < outs.n; ++d) ptx::tma_store_2d(&outs.map[d], stg_addr, n0 + sl * 64, m0w);
+              if (lane < outs.n) {
+                ptx::tma_store_2d(&outs.map[lane], stg_addr, n0 + sl * 64, m0w);
                 ptx::bulk_commit_group();
               }
             } else if (sl == SLABS - 1) {
               ptx::fence_proxy_async_smem();
               __syncwarp();
-              if (lane < SLABS) {
-                for (int d = 0; d < outs.n; ++d)
-                  ptx::tma_store_2d(&outs.map[d], stg_addr + lane * 4096, n0 + lane * 64, m0w);
+              if (lane < SLABS * outs.n) {
+                const int d = lane / SLABS, ls = lane % SLABS;
+                ptx::tma_store_2d(&outs.map[d], stg_addr + ls * 4096, n0 + ls * 64, m0w);
                 ptx::bulk_commit_group();
               }
             }
@@ -616,7 +619,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         }
       }
     }
-    if (!SWAP && lane < 2) ptx::bulk_wait_all();   // stores (also those to peer GPUs) are done
+    if (!SWAP && lane < 2 * kMaxOutTargets) ptx::bulk_wait_all();   // stores (also those to peer GPUs) are done
     __syncwarp();
   }
 
