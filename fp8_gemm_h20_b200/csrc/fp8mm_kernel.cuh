@@ -146,6 +146,45 @@ __device__ __forceinline__ void stage_scales(int tid, const UnitCoord& c, const 
   const float* as0 = p.As + (long long)kb0 * p.as_sk;
   const float* bs0 = p.Bs + (long long)(c.wi * (WT / 128)) * p.bs_sn + (long long)kb0 * p.bs_sk;
   const int total = kbn * TT;
+  // Row-major activation scales (unit stride along K, the layout the quantiser writes): four K
+  // blocks of a token per 16-byte load, a quarter of the load instructions and round trips.
+  if (p.as_sk == 1 && (p.as_sm & 3) == 0 && ((kb0 | kbn) & 3) == 0 &&
+      (reinterpret_cast<unsigned long long>(p.As) & 15ull) == 0) {
+    constexpr int UV = U / 4 > 0 ? U / 4 : 1;
+    const int quads = (kbn >> 2) * TT;
+    for (int base = tid; base < quads; base += NT * UV) {
+      float4 v[UV];
+#pragma unroll
+      for (int u = 0; u < UV; ++u) {
+        const int idx = base + u * NT;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (idx < quads) {
+          const int kq = idx / TT, x = idx % TT;
+          const int tok = min(t0 + x, p.M - 1);
+          v[u] = __ldg(reinterpret_cast<const float4*>(as0 + (long long)tok * p.as_sm + kq * 4));
+          if (SWAP) {
+            const float* b = bs0 + (long long)(kq * 4) * p.bs_sk;
+            v[u].x *= __ldg(b);
+            v[u].y *= __ldg(b + p.bs_sk);
+            v[u].z *= __ldg(b + 2 * p.bs_sk);
+            v[u].w *= __ldg(b + 3 * p.bs_sk);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UV; ++u) {
+        const int idx = base + u * NT;
+        if (idx < quads) {
+          const int kq = idx / TT, x = idx % TT;
+          float* dst = ta + (kq * 4) * TT + x;
+          dst[0] = v[u].x;
+          dst[TT] = v[u].y;
+          dst[2 * TT] = v[u].z;
+          dst[3 * TT] = v[u].w;
+        }
+      }
+    }
+  } else
   for (int base = tid; base < total; base += NT * U) {
     float v[U];
 #pragma unroll
@@ -244,7 +283,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(bar_full + 8 * s, 1);
-      ptx::mbar_init(bar_empty + 8 * s, 1);
+      ptx::mbar_init(bar_empty + 8 * s, KG);   // one tcgen05.commit per K block held by the slot
     }
     for (int b = 0; b < NBUF; ++b) {
       ptx::mbar_init(bar_tfull + 8 * b, 1);
@@ -352,8 +391,11 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
             ptx::umma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, k);
           }
           ptx::umma_commit(bar_tfull + 8 * buf);   // this K block's partial product is ready
-          // No second commit for the ring slot: a tcgen05.commit costs this thread ~250 cycles.
-          // The promotion warps see the same completion (tfull) and release the slot.
+          // A second commit hands the K block's operand tiles back to the producer once these MMAs
+          // have retired.  (A commit covers the MMAs of its own thread, i.e. exactly this block.)
+          // With two issuing threads there is time for it here, and it takes one barrier operation
+          // per K block off the promotion warps, whose pace every other role follows.
+          ptx::umma_commit(bar_empty + 8 * stage);
           if (j == KG - 1 && ++stage == stages) { stage = 0; ph ^= 1u; }
         }
       }
@@ -385,7 +427,6 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * CPT;
     const bool leader = threadIdx.x == kProducerThreads;
     uint32_t ui = 0, it = 0;
-    int pstage = 0;              // ring slot of the K block being promoted
     for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
       const UnitCoord c = decode_unit(u, p);
       const uint32_t t = ui & 1u, sph = (ui >> 1) & 1u;
@@ -409,12 +450,6 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         const float4* sv = reinterpret_cast<const float4*>(ta + kb * TT + half * CPT);
         const uint32_t tb_idx = buf;
         if (!bw.wait(bar_tfull + 8 * tb_idx, tph, kWaitPromoTmemFull)) { ok = false; break; }
-        // the MMAs of this K block (and, with two blocks per slot, of the one before: buffers are
-        // awaited in order) have retired, so the slot's operand tiles may be overwritten
-        if (KG == 1 || (it & 1u)) {
-          if (leader) ptx::mbar_arrive(bar_empty + 8 * pstage);
-          if (++pstage == stages) pstage = 0;
-        }
         ptx::tc_fence_after();
         const uint32_t taddr = lane_base + buf * UMMA_N;
 #define FP8MM_PROMOTE_CHUNK(dd_, ch_)                                                              \
@@ -574,7 +609,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           const int nsl = p.stg_slabs;
           unsigned char* stg = staging_ptr + pw * 4096 * nsl;
           const uint32_t stg_addr = staging + pw * 4096 * nsl;
-          constexpr int SLABS = CPT / 64;
+          constexpr int SLABS = CPT >= 64 ? CPT / 64 : 1;
 #pragma unroll
           for (int sl = 0; sl < SLABS; ++sl) {
             const int so = (nsl == 2) ? sl * 4096 : 0;
