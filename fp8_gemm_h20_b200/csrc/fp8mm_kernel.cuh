@@ -283,7 +283,11 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(bar_full + 8 * s, 1);
-      ptx::mbar_init(bar_empty + 8 * s, KG);   // one tcgen05.commit per K block held by the slot
+      // Two arrivals hand a slot back to the producer.  One K block per slot: the commit of the
+      // thread that issued its MMAs, and a plain arrive of the other MMA thread once it has seen
+      // the slot full (otherwise the slot could be refilled before that thread looked, and its
+      // parity wait would be a whole ring pass off).  Two K blocks per slot: both threads' commits.
+      ptx::mbar_init(bar_empty + 8 * s, 2);
     }
     for (int b = 0; b < NBUF; ++b) {
       ptx::mbar_init(bar_tfull + 8 * b, 1);
@@ -373,7 +377,10 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
             // can only tell the current phase from the one before, and a slot whose previous fill
             // this thread had never seen complete could otherwise read as "already full".  (With
             // two blocks per slot each thread owns one block of every slot and waits on all.)
-            if (KG == 1 && !bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
+            if constexpr (KG == 1) {
+              if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
+              ptx::mbar_arrive(bar_empty + 8 * stage);     // seen: the slot may be refilled
+            }
             if (j == KG - 1 && ++stage == stages) { stage = 0; ph ^= 1u; }
             continue;
           }
