@@ -323,9 +323,11 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   BoundedWait bw{&ctl->abort, p.status, p.timeout_ns};
 
   // 384-thread variants: the four service warps hand registers to the eight promotion
-  // warps, which hold 128 accumulators plus two TMEM load buffers each.
+  // warps, which hold 128 accumulators plus two TMEM load buffers each.  The launch allocates
+  // 168 per thread; 128 x (168 - 56) released = 256 x (224 - 168) taken.  At 216 the promotion
+  // loop spilled a few values and the packed FMA's register pairs did not fit.
   if (warp < 4) {
-  if constexpr (CPT == 128) ptx::setmaxnreg_dec<64>();
+  if constexpr (CPT == 128) ptx::setmaxnreg_dec<56>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -426,7 +428,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   }
   } else {
     // ------------------------------------------------- promotion + epilogue warps
-    if constexpr (CPT == 128) ptx::setmaxnreg_inc<216>();
+    if constexpr (CPT == 128) ptx::setmaxnreg_inc<224>();
     const int pw = warp - 4;
     const int q = warp & 3;      // TMEM lane quarter this warp may read
     const int half = pw >> 2;    // which 128-column half of a 256-wide tile
@@ -459,19 +461,24 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         if (!bw.wait(bar_tfull + 8 * tb_idx, tph, kWaitPromoTmemFull)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t taddr = lane_base + buf * UMMA_N;
+// One pair of accumulator columns: the packed FP32 FMA takes half the issue slots of two fmaf and
+// gives the same bits.  The promotion warps share their SM sub-partition's issue port with one
+// another and with the service warps, and their FMAs were half of all instructions issued.
+#define FP8MM_FMA_PAIR(a0_, a1_, d0_, d1_, s0_, s1_) ptx::ffma2(a0_, a1_, d0_, d1_, s0_, s1_)
 #define FP8MM_PROMOTE_CHUNK(dd_, ch_)                                                              \
   do {                                                                                             \
     if (SWAP) {                                                                                    \
       _Pragma("unroll") for (int i_ = 0; i_ < CH; i_ += 4) {                                       \
         const float4 s4_ = sv[((ch_) * CH + i_) >> 2];                                             \
-        acc[(ch_) * CH + i_ + 0] = fmaf(__uint_as_float(dd_[i_ + 0]), s4_.x, acc[(ch_) * CH + i_ + 0]); \
-        acc[(ch_) * CH + i_ + 1] = fmaf(__uint_as_float(dd_[i_ + 1]), s4_.y, acc[(ch_) * CH + i_ + 1]); \
-        acc[(ch_) * CH + i_ + 2] = fmaf(__uint_as_float(dd_[i_ + 2]), s4_.z, acc[(ch_) * CH + i_ + 2]); \
-        acc[(ch_) * CH + i_ + 3] = fmaf(__uint_as_float(dd_[i_ + 3]), s4_.w, acc[(ch_) * CH + i_ + 3]); \
+        FP8MM_FMA_PAIR(acc[(ch_) * CH + i_], acc[(ch_) * CH + i_ + 1], dd_[i_], dd_[i_ + 1],       \
+                       s4_.x, s4_.y);                                                              \
+        FP8MM_FMA_PAIR(acc[(ch_) * CH + i_ + 2], acc[(ch_) * CH + i_ + 3], dd_[i_ + 2],            \
+                       dd_[i_ + 3], s4_.z, s4_.w);                                                 \
       }                                                                                            \
     } else {                                                                                       \
-      _Pragma("unroll") for (int i_ = 0; i_ < CH; ++i_)                                            \
-        acc[(ch_) * CH + i_] = fmaf(__uint_as_float(dd_[i_]), sc, acc[(ch_) * CH + i_]);           \
+      _Pragma("unroll") for (int i_ = 0; i_ < CH; i_ += 2)                                         \
+        FP8MM_FMA_PAIR(acc[(ch_) * CH + i_], acc[(ch_) * CH + i_ + 1], dd_[i_], dd_[i_ + 1], sc,   \
+                       sc);                                                                        \
     }                                                                                              \
   } while (0)
         uint32_t d[2][CH];
@@ -508,6 +515,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           FP8MM_PROMOTE_CHUNK(d[1], 3);
         }
 #undef FP8MM_PROMOTE_CHUNK
+#undef FP8MM_FMA_PAIR
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_scempty + 8 * t);
