@@ -687,27 +687,63 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       const int j0 = half * CPT + (int)ptx::cluster_ctarank() * cps;
       const uint32_t red0 = ring + ((uint32_t)j0 * 128u + (uint32_t)row) * 4u;
       if (SWAP) {
-        const int n = c.wi * 128 + row;
-        for (int jj = 0; jj < cps; ++jj) {
-          float v = 0.f;
-          for (int s = 0; s < p.split; ++s) {
-            const float x = ptx::ld_cluster_f32(ptx::map_to_cta(red0 + jj * 512, s));
-            v = s == 0 ? x : v + x;
+        // The partial tiles lie column-major ([token column][128 weight rows]), and any rank may
+        // reduce any column as long as the additions run in rank order.  Rank r takes the columns
+        // [r, r+1) * UMMA_N / split; a warp takes whole columns, a lane four consecutive weight
+        // rows: one 16-byte distributed-shared-memory load per rank and column (a quarter of the
+        // requests of scalar loads, all ranks of two columns in flight together) and one 8-byte
+        // store of four bf16, 256 contiguous bytes per warp.
+        const int cpr = UMMA_N / p.split;
+        const int col0 = (int)ptx::cluster_ctarank() * cpr;
+        const uint32_t rbase = ring + (uint32_t)(4 * lane) * 4u;
+        const int n = c.wi * 128 + 4 * lane;
+        for (int i = pw; i < cpr; i += 2 * NPW) {
+          float4 x[2][8];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+              x[u][s] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (s < p.split && i + u * NPW < cpr)
+                x[u][s] = ptx::ld_cluster_f32x4(ptx::map_to_cta(rbase + (uint32_t)(col0 + i + u * NPW) * 512u, s));
+            }
           }
-          const int m = c.ti * TT + j0 + jj;
-          if (m < p.M)
-            for (int d = 0; d < outs.n; ++d) outs.ptr[d][(long long)m * p.ldc + n] = __float2bfloat16_rn(v);
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            float4 v = x[u][0];
+#pragma unroll
+            for (int s = 1; s < 8; ++s) {
+              if (s < p.split) {
+                v.x += x[u][s].x;
+                v.y += x[u][s].y;
+                v.z += x[u][s].z;
+                v.w += x[u][s].w;
+              }
+            }
+            const int m = c.ti * TT + col0 + i + u * NPW;
+            if (i + u * NPW < cpr && m < p.M) {
+              __nv_bfloat162 b0 = __floats2bfloat162_rn(v.x, v.y), b1 = __floats2bfloat162_rn(v.z, v.w);
+              uint2 o;
+              o.x = *reinterpret_cast<uint32_t*>(&b0);
+              o.y = *reinterpret_cast<uint32_t*>(&b1);
+              for (int d = 0; d < outs.n; ++d)
+                *reinterpret_cast<uint2*>(outs.ptr[d] + (long long)m * p.ldc + n) = o;
+            }
+          }
         }
       } else {
         const int m = c.ti * 128 + row;
         for (int jj = 0; jj < cps; jj += 8) {
           float v[8];
-          for (int s = 0; s < p.split; ++s) {
+          for (int s = 0; s < p.split; s += 2) {     // two ranks per round: sixteen loads in flight
+            float xa[8], xb[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const float x = ptx::ld_cluster_f32(ptx::map_to_cta(red0 + (jj + i) * 512, s));
-              v[i] = s == 0 ? x : v[i] + x;
+              xa[i] = ptx::ld_cluster_f32(ptx::map_to_cta(red0 + (jj + i) * 512, s));
+              xb[i] = ptx::ld_cluster_f32(ptx::map_to_cta(red0 + (jj + i) * 512, s + 1));
             }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = (s == 0 ? xa[i] : v[i] + xa[i]) + xb[i];
           }
           const int n = c.wi * WT + j0 + jj;
           if (m < p.M && n < p.N) {
