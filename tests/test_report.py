@@ -28,6 +28,10 @@ def test_layer_mix_needs_every_shape():
     shapes = [dict(N=256, K=128, count=3), dict(N=128, K=128, count=2)]
     rows = [dict(M=1, N=256, K=128, us=2.0), dict(M=1, N=128, K=128, us=1.0), dict(M=8, N=256, K=128, us=5.0)]
     assert report.layer_mix(rows, shapes) == {1: 8.0}
+    # two layers with the same (N, K): counts add up, duplicate rows are ignored
+    shapes.append(dict(N=128, K=128, count=5))
+    rows.append(dict(M=1, N=128, K=128, us=1.0))
+    assert report.layer_mix(rows, shapes) == {1: 13.0}
 
 
 def test_markdown_and_summary_render():
