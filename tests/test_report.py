@@ -46,3 +46,20 @@ def test_markdown_and_summary_render():
     assert "| 12288 | 2048 | 8192 | 221.00 |" in md and "Two concurrent streams" in md and "cold us" in md
     assert any("M >= 4096" in k for k in rep["summary"]) and any("M <= 64" in k for k in rep["summary"])
     json.dumps(rep)
+
+
+def test_render_rebuilds_report_from_saved_json(tmp_path):
+    measured = dict(hbm_gbs=6532.2, fp8_tflops=2760.8)
+    pts = []
+    for (n, k) in [(12288, 2048), (2048, 4096), (9216, 2048), (2048, 4096), (1024, 2048), (2048, 512)]:
+        pts.append(report.point_row(8192, n, k, 100.0, None, measured))      # (2048, 4096) twice, as two layers
+    saved = dict(profile="35b_tp1", device="x", rounds=5, command="c", measured_peaks=measured, clocks={},
+                 points=pts, layer_mix_us={}, two_streams=[], summary={})
+    src = tmp_path / "saved.json"
+    src.write_text(json.dumps(saved))
+    assert report.main(["--profile", "35b_tp1", "--render", str(src), "--out", str(tmp_path / "out")]) == 0
+    rep = json.loads((tmp_path / "out.json").read_text())
+    assert len(rep["points"]) == 5
+    # counts of the 35B profile: 30 + (30 + 10) + 10 + 40 + 40 layers, 100 us each
+    assert rep["layer_mix_us"] == {"8192": 16000.0} or rep["layer_mix_us"] == {8192: 16000.0}
+    assert "| 8192 | 16000.0 |" in (tmp_path / "out.md").read_text()
