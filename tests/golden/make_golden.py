@@ -3,7 +3,7 @@
 Run in the build container only (needs the reference checkout; nothing here is read at
 test time except the files it writes):
 
-    cd /tmp && python <repo>/tests/golden/make_golden.py --reference /root/reference
+    cd /tmp && python <repo>/tests/golden/make_golden.py --reference <reference checkout>
 
 1. gemm_golden.npz — for a handful of small seeded problems, the outputs of the reference's
    `reference()` and `error()` (scripts/validate.py:32-37) and `ref()` (bench.py:25-30),
@@ -80,7 +80,7 @@ def synthetic_tables():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     a = ap.parse_args()
     sys.path.insert(0, a.reference)
     import numpy as np
