@@ -115,7 +115,9 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   if (stages < 2) return FP8MM_E_CONFIG;
   g->stages = stages;
   // the cluster reduction parks the fp32 partial tile in the (then idle) operand ring
-  if (g->cluster && (size_t)stages * stage_bytes < (size_t)g->umma_n * 128 * sizeof(float)) g->cluster = false;
+  // (token-major tiles park it row-major with rows padded by four floats)
+  if (g->cluster && (size_t)stages * stage_bytes < (size_t)(g->umma_n + (g->swap ? 0 : 4)) * 128 * sizeof(float))
+    g->cluster = false;
   size_t smem = fixed + stages * stage_bytes;
   // Shared memory share >= TMEM share, so that CTAs that fit on an SM together (this
   // kernel's or another stream's) can never ask for more than the 512 TMEM columns.

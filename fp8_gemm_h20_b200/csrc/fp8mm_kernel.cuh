@@ -524,10 +524,20 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       if constexpr (SPLITK == 2) {
         // Cluster split-K: park the fp32 partial in this CTA's own shared memory (the operand ring
         // is idle: this CTA's only unit is finished); the reduction follows the cluster barrier.
+        // Swap-AB tiles park column-major ([token column][128 weight rows], the output's order);
+        // token-major tiles park row-major with rows padded by four floats, so that the 16-byte
+        // stores here and the 16-byte loads of the reduction are free of bank conflicts.
         if (ok) {
-          float* red = reinterpret_cast<float*>(smem) + (size_t)(half * CPT) * 128 + row;
+          if constexpr (SWAP) {
+            float* red = reinterpret_cast<float*>(smem) + (size_t)(half * CPT) * 128 + row;
 #pragma unroll
-          for (int j = 0; j < CPT; ++j) red[j * 128] = acc[j];
+            for (int j = 0; j < CPT; ++j) red[j * 128] = acc[j];
+          } else {
+            float4* red = reinterpret_cast<float4*>(reinterpret_cast<float*>(smem) +
+                                                    (size_t)row * (UMMA_N + 4) + half * CPT);
+#pragma unroll
+            for (int j = 0; j < CPT; j += 4) red[j >> 2] = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+          }
         }
         break;
       } else if constexpr (SPLITK == 1) {
@@ -675,17 +685,14 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
 
   if constexpr (SPLITK == 2) {
     // ------------------------------------------------- cluster split-K reduction
-    // Rank r of the cluster reduces, for every row, the r-th slice of each column half over all
-    // ranks in rank order (the same order as the workspace path: bit-identical results) and
-    // writes those columns of the output.
+    // Rank r of the cluster reduces the r-th slice of the tile (token columns of a swap-AB tile,
+    // token rows of a token-major one) over all ranks in rank order (the same order as the
+    // workspace path: bit-identical results) and writes that slice of the output.
     __syncthreads();
     ptx::cluster_sync_all();             // every CTA's partial tile is in its shared memory
     if (warp >= 4 && blockIdx.x < p.num_units) {
       const UnitCoord c = decode_unit(blockIdx.x, p);
-      const int pw = warp - 4, q = warp & 3, half = pw >> 2, row = q * 32 + lane;
-      const int cps = CPT / p.split;     // columns of this half that this rank reduces
-      const int j0 = half * CPT + (int)ptx::cluster_ctarank() * cps;
-      const uint32_t red0 = ring + ((uint32_t)j0 * 128u + (uint32_t)row) * 4u;
+      const int pw = warp - 4;
       if (SWAP) {
         // The partial tiles lie column-major ([token column][128 weight rows]), and any rank may
         // reduce any column as long as the additions run in rank order.  Rank r takes the columns
@@ -732,30 +739,44 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           }
         }
       } else {
-        const int m = c.ti * 128 + row;
-        for (int jj = 0; jj < cps; jj += 8) {
-          float v[8];
-          for (int s = 0; s < p.split; s += 2) {     // two ranks per round: sixteen loads in flight
-            float xa[8], xb[8];
+        // Token-major tiles: rank r reduces the rows [r, r+1) * 128 / split; a warp takes whole rows,
+        // a lane four consecutive weight columns of each 128-column block: one 16-byte load per
+        // rank (all ranks of a row in flight together) and 8-byte stores, 256 contiguous bytes per
+        // warp.  The additions run in rank order, as on the workspace path.
+        const int rpr = 128 / p.split;
+        const int row0 = (int)ptx::cluster_ctarank() * rpr;
+        for (int i = pw; i < rpr; i += NPW) {
+          const int r = row0 + i;
+          const int m = c.ti * 128 + r;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              xa[i] = ptx::ld_cluster_f32(ptx::map_to_cta(red0 + (jj + i) * 512, s));
-              xb[i] = ptx::ld_cluster_f32(ptx::map_to_cta(red0 + (jj + i) * 512, s + 1));
+          for (int cb = 0; cb < UMMA_N / 128; ++cb) {
+            const int col = cb * 128 + 4 * lane;
+            const uint32_t addr = ring + ((uint32_t)r * (UMMA_N + 4) + (uint32_t)col) * 4u;
+            float4 x[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+              x[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (s < p.split) x[s] = ptx::ld_cluster_f32x4(ptx::map_to_cta(addr, s));
             }
+            float4 v = x[0];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = (s == 0 ? xa[i] : v[i] + xa[i]) + xb[i];
-          }
-          const int n = c.wi * WT + j0 + jj;
-          if (m < p.M && n < p.N) {
-            __nv_bfloat162 b0 = __floats2bfloat162_rn(v[0], v[1]), b1 = __floats2bfloat162_rn(v[2], v[3]);
-            __nv_bfloat162 b2 = __floats2bfloat162_rn(v[4], v[5]), b3 = __floats2bfloat162_rn(v[6], v[7]);
-            uint4 o;
-            o.x = *reinterpret_cast<uint32_t*>(&b0);
-            o.y = *reinterpret_cast<uint32_t*>(&b1);
-            o.z = *reinterpret_cast<uint32_t*>(&b2);
-            o.w = *reinterpret_cast<uint32_t*>(&b3);
-            for (int d = 0; d < outs.n; ++d)
-              *reinterpret_cast<uint4*>(outs.ptr[d] + (long long)m * p.ldc + n) = o;
+            for (int s = 1; s < 8; ++s) {
+              if (s < p.split) {
+                v.x += x[s].x;
+                v.y += x[s].y;
+                v.z += x[s].z;
+                v.w += x[s].w;
+              }
+            }
+            const int n = c.wi * WT + col;
+            if (m < p.M && n < p.N) {
+              __nv_bfloat162 b0 = __floats2bfloat162_rn(v.x, v.y), b1 = __floats2bfloat162_rn(v.z, v.w);
+              uint2 o;
+              o.x = *reinterpret_cast<uint32_t*>(&b0);
+              o.y = *reinterpret_cast<uint32_t*>(&b1);
+              for (int d = 0; d < outs.n; ++d)
+                *reinterpret_cast<uint2*>(outs.ptr[d] + (long long)m * p.ldc + n) = o;
+            }
           }
         }
       }
