@@ -17,6 +17,7 @@ LIB_PATH = _PKG / LIB_NAME
 IMPL_UMMA = 0
 IMPL_UMMA_SWAP = 1
 IMPL_UMMA_2CTA = 2
+IMPL_GEMV = 3
 E_DEVICE_TIMEOUT = -8
 E_TOO_LARGE = -9
 

@@ -13,7 +13,8 @@ from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
 SOURCES = [PKG / "csrc" / "fp8mm_b200.cu", PKG / "csrc" / "fp8mm_quant.cu"]
-HEADERS = [PKG / "csrc" / "fp8mm_kernel.cuh", PKG / "csrc" / "fp8mm_kernel_2cta.cuh", PKG / "csrc" / "ptx_sm100.cuh",
+HEADERS = [PKG / "csrc" / "fp8mm_kernel.cuh", PKG / "csrc" / "fp8mm_kernel_2cta.cuh", PKG / "csrc" / "fp8mm_gemv.cuh",
+           PKG / "csrc" / "ptx_sm100.cuh",
            PKG.parent / "include" / "fp8mm_b200.h"]
 OUT = PKG / "libfp8mm_b200.so"
 

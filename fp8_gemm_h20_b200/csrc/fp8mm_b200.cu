@@ -14,6 +14,7 @@
 #include "../../include/fp8mm_b200.h"
 #include "fp8mm_kernel.cuh"
 #include "fp8mm_kernel_2cta.cuh"
+#include "fp8mm_gemv.cuh"
 
 namespace fp8mm {
 namespace {
@@ -40,6 +41,7 @@ struct Geometry {
   size_t smem;
   int stg_slabs;
   int kg;              // K blocks per ring slot (1 or 2)
+  bool gemv;           // CUDA-core decode path: no tiles, no split, no scratch
   size_t counter_bytes, partial_bytes;
 };
 
@@ -59,6 +61,10 @@ int check_cfg(int M, int N, int K, const fp8mm_cfg* c) {
     if (!is_pow2(c->block_t) || c->block_t < 16 || c->block_t > 256) return FP8MM_E_CONFIG;
   } else if (c->impl == FP8MM_IMPL_UMMA_2CTA) {
     if (c->block_t != 256 || c->block_w != 256) return FP8MM_E_CONFIG;
+  } else if (c->impl == FP8MM_IMPL_GEMV) {
+    if (c->block_w != kGemvRows) return FP8MM_E_CONFIG;
+    if (c->block_t != 1 && c->block_t != 2 && c->block_t != 4) return FP8MM_E_CONFIG;
+    if ((M + c->block_t - 1) / c->block_t > 65535) return FP8MM_E_CONFIG;
   } else {
     return FP8MM_E_CONFIG;
   }
@@ -69,6 +75,13 @@ int check_cfg(int M, int N, int K, const fp8mm_cfg* c) {
 int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   const int rc = check_cfg(M, N, K, c);
   if (rc != FP8MM_OK) return rc;
+  memset(g, 0, sizeof(*g));
+  g->gemv = c->impl == FP8MM_IMPL_GEMV;
+  if (g->gemv) {             // one pass over the weights: nothing to legalise, no scratch
+    g->split = 1;
+    g->kb_total = g->kbn = K / 128;
+    return FP8MM_OK;
+  }
   g->swap = c->impl == FP8MM_IMPL_UMMA_SWAP;
   g->pair = c->impl == FP8MM_IMPL_UMMA_2CTA;
   g->umma_n = g->swap ? c->block_t : c->block_w;
@@ -233,7 +246,7 @@ int make_output_map(void* c, int m, int n, long long ldc, CUtensorMap* out) {
 // ----------------------------------------------------------------- launch
 struct DeviceInfo {
   int sms = 0;
-  bool attr_set[40] = {};
+  bool attr_set[40] = {};     // 0..35 tile kernels, 39 CTA-pair kernel
 };
 DeviceInfo g_dev[kMaxDevices];
 
@@ -359,6 +372,68 @@ int launch(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, cons
   return launch_one<UMMA_N, SWAP, 0>(3 * slot, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
 }
 
+// Decode path: grid and CTA shape from the problem alone (see fp8mm_gemv.cuh).
+template <int MT>
+int launch_gemv_mt(const GemvParams& p, dim3 grid, int warps, cudaStream_t stream) {
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = grid;
+  lc.blockDim = dim3(warps * 32);
+  lc.dynamicSmemBytes = 0;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int na = 0;
+  if (use_pdl()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  lc.attrs = attr;
+  lc.numAttrs = na;
+  const cudaError_t e = cudaLaunchKernelEx(&lc, fp8mm_gemv_kernel<MT>, p);
+  if (e != cudaSuccess) (void)cudaGetLastError();
+  return e == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
+}
+
+int launch_gemv(int dev, const fp8mm_args* a, const fp8mm_cfg* cfg, void* const* extra_c, int n_extra,
+                cudaStream_t stream) {
+  const int sms = g_dev[dev].sms;
+  const int mt = cfg->block_t;
+  (void)cfg->max_ctas;     // one item per warp: the grid is the problem
+  GemvParams p;
+  memset(&p, 0, sizeof(p));
+  p.A = static_cast<const unsigned char*>(a->A);
+  p.B = static_cast<const unsigned char*>(a->B);
+  p.As = a->As;
+  p.Bs = a->Bs;
+  p.n_out = 1 + n_extra;
+  for (int d = 0; d < p.n_out; ++d) p.out[d] = static_cast<__nv_bfloat16*>(d == 0 ? a->C : extra_c[d - 1]);
+  p.as_sm = a->as_stride_m;
+  p.as_sk = a->as_stride_k;
+  p.bs_sn = a->bs_stride_n;
+  p.bs_sk = a->bs_stride_k;
+  p.ldc = a->ldc;
+  p.M = a->M;
+  p.N = a->N;
+  p.K = a->K;
+  p.kb_total = a->K / 128;
+  p.n_kc = (p.kb_total + 3) / 4;
+  p.kw = p.n_kc < kGemvMaxWarps ? p.n_kc : kGemvMaxWarps;
+  p.n_rg = a->N / kGemvRows;
+  // row groups per CTA: as many as fit in eight warps, fewer while that leaves SMs without a CTA
+  int groups = kGemvMaxWarps / p.kw;
+  while (groups > 1 && (p.n_rg + groups - 1) / groups < 2 * sms) groups >>= 1;
+  p.groups = groups;
+  const int warps = p.kw * groups;
+  const int grid_x = (p.n_rg + groups - 1) / groups;
+  const dim3 grid(grid_x, (a->M + mt - 1) / mt);
+  switch (mt) {
+    case 1: return launch_gemv_mt<1>(p, grid, warps, stream);
+    case 2: return launch_gemv_mt<2>(p, grid, warps, stream);
+    case 4: return launch_gemv_mt<4>(p, grid, warps, stream);
+  }
+  return FP8MM_E_CONFIG;
+}
+
 }  // namespace
 }  // namespace fp8mm
 
@@ -445,6 +520,12 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
       return FP8MM_E_DRIVER;
     g_dev[dev].sms = sms;
+  }
+
+  if (g.gemv) {
+    for (int d = 0; d < n_extra; ++d)
+      if (extra_c[d] == nullptr) return FP8MM_E_NULL;
+    return launch_gemv(dev, a, cfg, extra_c, n_extra, static_cast<cudaStream_t>(stream_));
   }
 
   CUtensorMap tm_tok, tm_wgt;

@@ -20,6 +20,9 @@ KERNELS = {
                                         "GROUP_SIZE_M": 8, "MAX_CTAS": 0}),
     "umma_swap": (_lib.IMPL_UMMA_SWAP, {"BLOCK_T": 16, "BLOCK_W": 128, "NUM_STAGES": 8, "SPLIT": 1,
                                         "GROUP_SIZE_M": 1, "MAX_CTAS": 0}),
+    # decode: BLOCK_T tokens per warp (1, 2 or 4), eight weight rows per warp step, FP32 FMAs
+    "gemv": (_lib.IMPL_GEMV, {"BLOCK_T": 1, "BLOCK_W": 8, "NUM_STAGES": 1, "SPLIT": 1,
+                              "GROUP_SIZE_M": 1, "MAX_CTAS": 0}),
 }
 
 _MIN_WORKSPACE = 1 << 20          # bytes; grown on demand, never shrunk

@@ -42,6 +42,11 @@ extern "C" {
 #define FP8MM_IMPL_UMMA        0    /* tokens on the 128 UMMA rows, weights on UMMA-N (128|256)  */
 #define FP8MM_IMPL_UMMA_SWAP   1    /* swap-AB: weights on the 128 UMMA rows, tokens on UMMA-N   */
 #define FP8MM_IMPL_UMMA_2CTA   2    /* CTA pairs (cta_group::2): 256 tokens x 256 weights per pair */
+#define FP8MM_IMPL_GEMV        3    /* decode (one to a handful of tokens): weight rows streamed straight
+                                       into registers, FP32 FMAs, 8 weight rows x 512 bytes of K per warp
+                                       step; no tensor memory, no barriers, no tensor maps.  Successor of
+                                       the reference's smallest tiles (BT=8, BW=16..128, kernel_v2.py:94-291
+                                       with the M<=8 entries of configs/122b_tp4.json)               */
 
 /* cfg.flags: reduce split-K partials through the global workspace even where the cluster
  * (distributed shared memory) reduction is available (splits of 2, 4 and 8). */
@@ -78,8 +83,9 @@ typedef struct fp8mm_args {
 /*
  * Launch configuration = one "config" object of a tuning-table entry
  * (fp8_gemm_h20/configs/*.json, "entries"/"N,K"/"M"/{"impl","config"}).
- *   block_t   token tile   (BLOCK_T):  UMMA   -> 128;  UMMA_SWAP -> 16,32,64,128,256;  UMMA_2CTA -> 256
- *   block_w   weight tile  (BLOCK_W):  UMMA   -> 128 or 256;  UMMA_SWAP -> 128;  UMMA_2CTA -> 256
+ *   block_t   token tile   (BLOCK_T):  UMMA   -> 128;  UMMA_SWAP -> 16,32,64,128,256;  UMMA_2CTA -> 256;
+ *             GEMV -> 1, 2 or 4 tokens per warp (more tokens run as further token groups)
+ *   block_w   weight tile  (BLOCK_W):  UMMA   -> 128 or 256;  UMMA_SWAP -> 128;  UMMA_2CTA -> 256;  GEMV -> 8
  *   stages    depth of the TMA shared-memory ring (NUM_STAGES); clipped to what fits
  *   split     split-K factor (SPLIT); a value that does not divide K/128 is
  *             legalised to 1, as the reference wrapper does (kernel_v2.py:355-356)
