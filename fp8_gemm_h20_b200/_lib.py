@@ -32,6 +32,7 @@ SYMBOLS = (
     "fp8mm_b200_quantize_act",
     "fp8mm_b200_expand_ue8m0",
     "fp8mm_b200_static_scratch_bytes",
+    "fp8mm_b200_static_scratch_status",
     "fp8mm_b200_last_status",
     "fp8mm_b200_strerror",
     "fp8mm_b200_version",
@@ -104,6 +105,8 @@ def load():
         lib.fp8mm_b200_expand_ue8m0.restype = ctypes.c_int
         lib.fp8mm_b200_static_scratch_bytes.argtypes = []
         lib.fp8mm_b200_static_scratch_bytes.restype = ctypes.c_size_t
+        lib.fp8mm_b200_static_scratch_status.argtypes = [ctypes.POINTER(ctypes.c_int32)]
+        lib.fp8mm_b200_static_scratch_status.restype = ctypes.c_int
         lib.fp8mm_b200_last_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         lib.fp8mm_b200_last_status.restype = ctypes.c_int
         lib.fp8mm_b200_strerror.argtypes = [ctypes.c_int]

@@ -26,6 +26,7 @@ constexpr int kMaxSplitTiles = 16384;
 constexpr size_t kCounterBytes = (size_t)kMaxSplitTiles * sizeof(int);
 constexpr size_t kMaxDynSmem = 232448;       // 227 KB opt-in dynamic shared memory per CTA
 constexpr int kMaxDevices = 64;
+constexpr int kClusterUnschedulable = -100;   // internal: the cluster launch has no room, use the workspace
 
 
 struct Geometry {
@@ -187,8 +188,21 @@ std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 // outside the tensor.  The encoding depends only on (pointer, shape, box): cached.
 // kg = 2: the same bytes seen as a 3-D tensor (128 bytes, rows, K blocks) with a box of two K
 // blocks, so that one copy delivers two consecutive operand tiles.
-int get_tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* out, int kg = 1) {
-  const MapKey key{ptr, rows, k, box_rows | (kg << 16)};
+// Test hook (host side): FP8MM_TEST_SHORT_WEIGHT_BOX=1 encodes the WEIGHT operand's map with half the
+// box rows, so that every weight copy delivers fewer bytes than the producer announced and the ring's
+// `full` barrier never completes.  With a short FP8MM_TIMEOUT_MS the bounded waits then run out, the
+// kernel records why and returns: the way the give-up path is exercised without a fault, a trap or an
+// endless wait.  Read at every encode, so a test can switch it off again (maps are cached per pointer).
+bool test_short_weight_box() {
+  const char* e = getenv("FP8MM_TEST_SHORT_WEIGHT_BOX");
+  return e != nullptr && e[0] == '1';
+}
+
+int get_tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* out, int kg = 1,
+                   bool weight = false) {
+  const bool shorten = weight && test_short_weight_box();
+  if (shorten) box_rows /= 2;
+  const MapKey key{ptr, rows, k, box_rows | (kg << 16) | (shorten ? 1 << 30 : 0)};
   {
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_maps.find(key);
@@ -229,8 +243,35 @@ int get_tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* 
 }
 
 // bf16 C [M, N] with row stride ldc, box = 32 rows x 64 columns (128 bytes), 128-byte swizzle.
-// Not cached: the output pointer is new on almost every call.
+// Cached by (pointer, M, N, ldc) like the operand maps: a caching allocator hands the same output
+// addresses out again and again, and an encode costs about as much as the rest of the host path.
+struct OutKey {
+  const void* ptr;
+  int m, n;
+  long long ldc;
+  bool operator==(const OutKey& o) const { return ptr == o.ptr && m == o.m && n == o.n && ldc == o.ldc; }
+};
+struct OutKeyHash {
+  size_t operator()(const OutKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h ^= (size_t)k.m * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h ^= (size_t)k.n * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
+    h ^= (size_t)k.ldc * 0x165667B19E3779F9ull + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+std::unordered_map<OutKey, CUtensorMap, OutKeyHash> g_out_maps;
+
 int make_output_map(void* c, int m, int n, long long ldc, CUtensorMap* out) {
+  const OutKey key{c, m, n, ldc};
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_out_maps.find(key);
+    if (it != g_out_maps.end()) {
+      *out = it->second;
+      return FP8MM_OK;
+    }
+  }
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return FP8MM_E_DRIVER;
   cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)m};
@@ -240,13 +281,22 @@ int make_output_map(void* c, int m, int n, long long ldc, CUtensorMap* out) {
   const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? FP8MM_OK : FP8MM_E_DRIVER;
+  if (r != CUDA_SUCCESS) return FP8MM_E_DRIVER;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_out_maps.size() > 8192) g_out_maps.clear();
+    g_out_maps.emplace(key, *out);
+  }
+  return FP8MM_OK;
 }
 
 // ----------------------------------------------------------------- launch
 struct DeviceInfo {
   int sms = 0;
   bool attr_set[40] = {};     // 0..35 tile kernels, 39 CTA-pair kernel
+  // cluster split-K kernels: can a cluster of 2 / 4 / 8 such CTAs be placed at all?  0 = not asked
+  // yet, 1 = yes, 2 = no (an SM-limited context, MPS or a green context can say no)
+  unsigned char cluster_ok[40][4] = {};
 };
 DeviceInfo g_dev[kMaxDevices];
 
@@ -304,6 +354,23 @@ int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, 
   }
   lc.attrs = attr;
   lc.numAttrs = na;
+  if (SPLITK == 2) {
+    const int si = g.split == 2 ? 0 : (g.split == 4 ? 1 : 2);
+    unsigned char known;
+    {
+      std::lock_guard<std::mutex> lk(g_mu);
+      known = g_dev[dev].cluster_ok[slot][si];
+    }
+    if (known == 0) {
+      int n = 0;
+      const cudaError_t q = cudaOccupancyMaxActiveClusters(&n, kern, &lc);
+      if (q != cudaSuccess) (void)cudaGetLastError();
+      known = (q == cudaSuccess && n > 0) ? 1 : 2;
+      std::lock_guard<std::mutex> lk(g_mu);
+      g_dev[dev].cluster_ok[slot][si] = known;
+    }
+    if (known == 2) return kClusterUnschedulable;
+  }
   const cudaError_t e = cudaLaunchKernelEx(&lc, kern, tm_tok, tm_wgt, outs, p);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return e == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
@@ -357,16 +424,25 @@ int launch(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, cons
     if (g.kg == 2) {          // slots 21..29: the two-K-blocks-per-slot variants of the narrow tiles
       const int s2 = 21 + 3 * slot;
       if (g.split > 1) {
-        if (g.cluster)
-          return launch_one<UMMA_N, SWAP, 2, 2>(s2 + 2, dev, g, tm_tok, tm_wgt, outs, p, p.num_units, stream);
+        if (g.cluster) {
+          const int rc = launch_one<UMMA_N, SWAP, 2, 2>(s2 + 2, dev, g, tm_tok, tm_wgt, outs, p, p.num_units, stream);
+          if (rc != kClusterUnschedulable) return rc;
+          if (p.ws_partial == nullptr) return FP8MM_E_WORKSPACE;
+        }
         return launch_one<UMMA_N, SWAP, 1, 2>(s2 + 1, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
       }
       return launch_one<UMMA_N, SWAP, 0, 2>(s2, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
     }
   }
   if (g.split > 1) {
-    if (g.cluster)
-      return launch_one<UMMA_N, SWAP, 2>(3 * slot + 2, dev, g, tm_tok, tm_wgt, outs, p, p.num_units, stream);
+    if (g.cluster) {
+      // No room for a cluster of `split` CTAs in this context: the workspace reduction gives the same
+      // bits, provided the caller's workspace is large enough for it (fp8mm_b200_workspace_bytes with
+      // FP8MM_FLAG_WORKSPACE_SPLIT set says how large).
+      const int rc = launch_one<UMMA_N, SWAP, 2>(3 * slot + 2, dev, g, tm_tok, tm_wgt, outs, p, p.num_units, stream);
+      if (rc != kClusterUnschedulable) return rc;
+      if (p.ws_partial == nullptr) return FP8MM_E_WORKSPACE;
+    }
     return launch_one<UMMA_N, SWAP, 1>(3 * slot + 1, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
   }
   return launch_one<UMMA_N, SWAP, 0>(3 * slot, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
@@ -439,8 +515,8 @@ int launch_gemv(int dev, const fp8mm_args* a, const fp8mm_cfg* cfg, void* const*
 
 // ----------------------------------------------------- allocation-free entry point
 // Scratch for callers that cannot allocate: status word, split-K tile counters and fp32 partial
-// tiles in a buffer that is part of the library image.  Zero at load; counters are re-zeroed by
-// every call.  In host code `g_static_scratch` is only a handle for cudaGetSymbolAddress — the
+// tiles in a buffer that is part of the library image.  Zero at load; the counters are re-zeroed by
+// every call, the status word stays until it is fetched.  In host code `g_static_scratch` is only a handle for cudaGetSymbolAddress — the
 // device address it yields is what the kernels receive.
 constexpr size_t kStaticScratchBytes = 8u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
@@ -489,8 +565,17 @@ int fp8mm_b200_workspace_init(void* workspace, size_t ws_bytes, void* stream) {
              : FP8MM_E_DRIVER;
 }
 
+static int static_scratch_address(void** out);
+
 int fp8mm_b200_last_status(const void* workspace, int32_t* detail) {
-  if (workspace == nullptr) return FP8MM_E_NULL;
+  if (workspace == nullptr) {
+    // callers of fp8mm_b200_gemm_static_scratch have no workspace pointer: NULL names the built-in
+    // scratch of the current device
+    void* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != FP8MM_OK) return rc;
+    workspace = scratch;
+  }
   int32_t v = 0;
   if (cudaMemcpy(&v, workspace, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return FP8MM_E_DRIVER;
   if (detail != nullptr) *detail = v;
@@ -531,7 +616,7 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
   CUtensorMap tm_tok, tm_wgt;
   rc = get_tensor_map(a->A, a->M, a->K, g.swap ? g.umma_n : 128, &tm_tok, g.kg);
   if (rc != FP8MM_OK) return rc;
-  rc = get_tensor_map(a->B, a->N, a->K, (g.swap || g.pair) ? 128 : g.umma_n, &tm_wgt, g.kg);
+  rc = get_tensor_map(a->B, a->N, a->K, (g.swap || g.pair) ? 128 : g.umma_n, &tm_wgt, g.kg, true);
   if (rc != FP8MM_OK) return rc;
 
   OutTargets outs;
@@ -554,8 +639,12 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
   p.Bs = a->Bs;
   p.C = static_cast<__nv_bfloat16*>(a->C);
   p.status = reinterpret_cast<int*>(ws);
-  p.ws_counter = (g.split > 1 && !g.cluster) ? reinterpret_cast<int*>(ws + kStatusBytes) : nullptr;
-  p.ws_partial = (g.split > 1 && !g.cluster) ? reinterpret_cast<float*>(ws + kStatusBytes + g.counter_bytes) : nullptr;
+  // split-K scratch: needed by the workspace reduction, and handed to a cluster launch too when the
+  // caller's workspace happens to be large enough, so that it can fall back if clusters have no room
+  const size_t ws_path_need = kStatusBytes + kCounterBytes + (size_t)g.tiles * g.split * g.umma_n * 128 * sizeof(float);
+  const bool ws_usable = g.split > 1 && ws != nullptr && ws_bytes >= ws_path_need;
+  p.ws_counter = ws_usable ? reinterpret_cast<int*>(ws + kStatusBytes) : nullptr;
+  p.ws_partial = ws_usable ? reinterpret_cast<float*>(ws + kStatusBytes + kCounterBytes) : nullptr;
   p.as_sm = a->as_stride_m;
   p.as_sk = a->as_stride_k;
   p.bs_sn = a->bs_stride_n;
@@ -620,28 +709,47 @@ int fp8mm_b200_gemm_bcast(const fp8mm_args* a, const fp8mm_cfg* cfg, void* works
 // ----------------------------------------------------- allocation-free entry point
 size_t fp8mm_b200_static_scratch_bytes(void) { return kStaticScratchBytes; }
 
+// Device address of the built-in scratch on the current device (looked up once per device).
+static int static_scratch_address(void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= fp8mm::kMaxDevices) return FP8MM_E_DRIVER;
+  std::lock_guard<std::mutex> lk(fp8mm::g_mu);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    // once per device, with that device current: symbol -> device address
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return FP8MM_E_DRIVER;
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return FP8MM_OK;
+}
+
 int fp8mm_b200_gemm_static_scratch(const fp8mm_args* args, const fp8mm_cfg* cfg, void* stream) {
   if (args == nullptr || cfg == nullptr) return FP8MM_E_NULL;
   const size_t need = fp8mm_b200_workspace_bytes(args->M, args->N, args->K, cfg);
   if (need == 0) return fp8mm_b200_validate(args->M, args->N, args->K, cfg);
   if (need > kStaticScratchBytes) return FP8MM_E_TOO_LARGE;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= fp8mm::kMaxDevices) return FP8MM_E_DRIVER;
   void* scratch = nullptr;
-  {
-    std::lock_guard<std::mutex> lk(fp8mm::g_mu);
-    if (g_static_scratch_addr[dev] == nullptr) {
-      // once per device, with that device current: symbol -> device address
-      void* p = nullptr;
-      if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return FP8MM_E_DRIVER;
-      g_static_scratch_addr[dev] = p;
-    }
-    scratch = g_static_scratch_addr[dev];
-  }
-  // status word + tile counters must start at zero whatever the previous call left behind
-  const size_t head = need < (size_t)(256 + 65536) ? need : (size_t)(256 + 65536);
-  if (cudaMemsetAsync(scratch, 0, head, static_cast<cudaStream_t>(stream)) != cudaSuccess) return FP8MM_E_DRIVER;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != FP8MM_OK) return rc;
+  // The tile counters must start at zero whatever the previous call left behind.  The status word in
+  // front of them is NOT cleared here: a timeout recorded by an earlier call stays readable
+  // (fp8mm_b200_static_scratch_status) until the caller has fetched it.
+  if (cudaMemsetAsync(static_cast<unsigned char*>(scratch) + kStatusBytes, 0, kCounterBytes,
+                      static_cast<cudaStream_t>(stream)) != cudaSuccess)
+    return FP8MM_E_DRIVER;
   return fp8mm_b200_gemm(args, cfg, scratch, kStaticScratchBytes, stream);
+}
+
+int fp8mm_b200_static_scratch_status(int32_t* detail) {
+  void* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc != FP8MM_OK) return rc;
+  int32_t v = 0;
+  if (cudaMemcpy(&v, scratch, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return FP8MM_E_DRIVER;
+  if (detail != nullptr) *detail = v;
+  if (v != 0 && cudaMemset(scratch, 0, sizeof(v)) != cudaSuccess) return FP8MM_E_DRIVER;   // fetched: start over
+  return v == 0 ? FP8MM_OK : FP8MM_E_DEVICE_TIMEOUT;
 }
 
 }  // extern "C"

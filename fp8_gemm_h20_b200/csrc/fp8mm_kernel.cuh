@@ -693,6 +693,16 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     if (warp >= 4 && blockIdx.x < p.num_units) {
       const UnitCoord c = decode_unit(blockIdx.x, p);
       const int pw = warp - 4;
+      // A rank whose bounded wait gave up has parked nothing: then no rank stores the tile.  The
+      // flags travel with the first batch of partial-tile loads (same round trip) and are looked
+      // at only where the stores are issued.
+      uint32_t bad = 0;
+      {
+        const uint32_t abort_addr = ptx::smem_u32(&ctl->abort);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          if (s < p.split) bad |= ptx::ld_cluster_u32(ptx::map_to_cta(abort_addr, s));
+      }
       if (SWAP) {
         // The partial tiles lie column-major ([token column][128 weight rows]), and any rank may
         // reduce any column as long as the additions run in rank order.  Rank r takes the columns
@@ -728,7 +738,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
               }
             }
             const int m = c.ti * TT + col0 + i + u * NPW;
-            if (i + u * NPW < cpr && m < p.M) {
+            if (i + u * NPW < cpr && m < p.M && bad == 0) {
               __nv_bfloat162 b0 = __floats2bfloat162_rn(v.x, v.y), b1 = __floats2bfloat162_rn(v.z, v.w);
               uint2 o;
               o.x = *reinterpret_cast<uint32_t*>(&b0);
@@ -769,7 +779,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
               }
             }
             const int n = c.wi * WT + col;
-            if (m < p.M && n < p.N) {
+            if (m < p.M && n < p.N && bad == 0) {
               __nv_bfloat162 b0 = __floats2bfloat162_rn(v.x, v.y), b1 = __floats2bfloat162_rn(v.z, v.w);
               uint2 o;
               o.x = *reinterpret_cast<uint32_t*>(&b0);

@@ -121,9 +121,14 @@ extern "C" int fp8mm_b200_expand_ue8m0(const void* src, float* dst, int32_t rows
   if (src == nullptr || dst == nullptr) return FP8MM_E_NULL;
   if (rows < 1 || kblocks < 1) return FP8MM_E_SHAPE;
   if (packed4 != 0 && (reinterpret_cast<uintptr_t>(src) & 3)) return FP8MM_E_ALIGN;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+    return FP8MM_E_DRIVER;
   const long long total = (long long)rows * kblocks;
   long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  const long long cap = (long long)sms * 8;               // 8 resident CTAs of 256 threads per SM
+  if (blocks > cap) blocks = cap;
   expand_ue8m0_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src), dst, rows, kblocks, row_stride, col_stride, packed4);
   return cudaGetLastError() == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;

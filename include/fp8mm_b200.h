@@ -91,6 +91,10 @@ typedef struct fp8mm_args {
  *             legalised to 1, as the reference wrapper does (kernel_v2.py:355-356)
  *   group_m   token tiles per raster group (GROUP_SIZE_M), >=1
  *   max_ctas  0 = one wave sized from the SM count; otherwise an upper bound on the grid
+ * A cluster launch needs room for `split` co-scheduled CTAs; where the context has none (an
+ * SM-limited or partitioned context) the call falls back to the workspace reduction if the
+ * workspace passed in is large enough for it (ask fp8mm_b200_workspace_bytes with
+ * FP8MM_FLAG_WORKSPACE_SPLIT set), else it returns FP8MM_E_WORKSPACE.
  * Split-K partials are reduced in split order, either by the CTA that arrives last on a
  * per-tile counter (workspace path, kernel_v2.py:274-289) or, for splits of 2, 4 and 8, by the
  * `split` CTAs of the tile themselves, launched as one thread-block cluster and reading each
@@ -159,8 +163,10 @@ int fp8mm_b200_gemm_bcast(const fp8mm_args* args, const fp8mm_cfg* cfg, void* wo
  *     non-allocating runtime query, done with that device current).  Make that first call
  *     before starting any stream capture on the device.
  *   - The buffer is shared by all calls and keeps what the last call left in it.  Each call
- *     re-zeroes the status word and the tile counters on `stream` before its kernel; the
- *     partial tiles are always written before they are read.
+ *     re-zeroes the tile counters on `stream` before its kernel; the partial tiles are always
+ *     written before they are read.  The status word (a bounded device-side wait that gave up)
+ *     is left alone, so that it can still be read after later calls:
+ *     fp8mm_b200_static_scratch_status().
  *   - Because it is one shared buffer, two calls that can overlap on the GPU (different
  *     streams, or different host threads on different streams) race on it.  Serialise them on
  *     one stream, or use fp8mm_b200_gemm with one workspace per stream.
@@ -171,6 +177,13 @@ int fp8mm_b200_gemm_static_scratch(const fp8mm_args* args, const fp8mm_cfg* cfg,
 
 /* Size in bytes of the built-in scratch buffer used by fp8mm_b200_gemm_static_scratch. */
 size_t fp8mm_b200_static_scratch_bytes(void);
+
+/* Status of the calls made through fp8mm_b200_gemm_static_scratch on the current device since
+ * the last time this was asked (synchronise the stream first): 0, or FP8MM_E_DEVICE_TIMEOUT with
+ * the role/barrier code in *detail (optional); a non-zero status is cleared by reading it.
+ * Blocking, allocates nothing.  No counterpart in the reference.  fp8mm_b200_last_status(NULL, ..)
+ * reads the same word without clearing it. */
+int fp8mm_b200_static_scratch_status(int32_t* detail);
 
 /* Activation quantiser, the step in front of the GEMM: bf16 X[M,K] (row stride ldx) ->
  * e4m3 A[M,K] (contiguous) and fp32 As[M,K/128] (any strides): per 1x128 group
@@ -195,7 +208,9 @@ int fp8mm_b200_expand_ue8m0(const void* src, float* dst, int32_t rows, int32_t k
 
 /* After the stream has been synchronised: 0 if no bounded device-side wait gave
  * up since the workspace was initialised, else FP8MM_E_DEVICE_TIMEOUT; *detail
- * (optional) receives the role/barrier code recorded by the kernel.  Blocking. */
+ * (optional) receives the role/barrier code recorded by the kernel.  Blocking.
+ * workspace == NULL names the built-in scratch of the current device (the one
+ * fp8mm_b200_gemm_static_scratch uses). */
 int fp8mm_b200_last_status(const void* workspace, int32_t* detail);
 
 /* Text for an error code. */

@@ -19,7 +19,9 @@ def _worker(rank, world, port, q):
     from fp8_gemm_h20_b200 import engine, sharded, testing
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=120))
     try:
         ok = True
         for m, n, k in [(37, 1024, 512), (300, 2048, 1024)]:
@@ -57,7 +59,43 @@ def test_two_gpu_gather_equals_single_gpu_result():
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(300)
-        assert p.exitcode == 0
+    try:
+        for p in procs:
+            p.join(300)
+    finally:
+        # a rank that hangs must not keep holding a GPU of the shared machine after the test
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+            if p.is_alive():
+                p.kill()
+                p.join(10)
+    assert [p.exitcode for p in procs] == [0, 0]
     assert dict(q.get(timeout=5) for _ in range(2)) == {0: True, 1: True}
+
+
+@pytest.mark.parametrize("impl,conf,m", [
+    ("umma", dict(BLOCK_W=256), 300),                              # TMA-store epilogue, two slabs
+    ("umma", dict(BLOCK_W=128, SPLIT=2), 200),                     # cluster split-K, plain stores
+    ("umma", dict(BLOCK_W=128, SPLIT=2, SPLIT_VIA_WORKSPACE=True), 200),
+    ("umma_swap", dict(BLOCK_T=64, SPLIT=1), 37),                  # swap-AB store loop
+    ("umma_swap", dict(BLOCK_T=32, SPLIT=4), 17),                  # swap-AB cluster reduction
+    ("umma_2cta", dict(), 512),
+])
+def test_multi_target_epilogue_on_one_gpu(impl, conf, m):
+    """fp8mm_b200_gemm_bcast with the extra targets on the SAME GPU: every epilogue variant must put
+    the same tiles into all targets (this is the only fused-path coverage a single-GPU run has)."""
+    from fp8_gemm_h20_b200 import engine, testing
+    n, k = 1024, 1024
+    A, B, As, Bs = (t.cuda() for t in testing.make_problem(m, n, k, seed=7))
+    want = engine.launch(A, B, As, Bs, impl, conf)
+    wide = [torch.full((m, 3 * n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    lo = n          # the shard's column slice inside a wider output
+    engine.launch(A, B, As, Bs, impl, conf, out=wide[0][:, lo:lo + n],
+                  also_to=[w[:, lo:lo + n].data_ptr() for w in wide[1:]])
+    torch.cuda.synchronize()
+    for w in wide:
+        assert torch.equal(w[:, lo:lo + n], want)
+        assert torch.isnan(w[:, :lo]).all() and torch.isnan(w[:, lo + n:]).all()
+    assert engine.device_status() == (0, 0)

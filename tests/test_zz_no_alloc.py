@@ -53,6 +53,37 @@ def test_static_scratch_matches_regular_entry_point_twice(m, n, k, impl, conf):
         torch.cuda.synchronize()
         assert torch.equal(out, want), (call, impl, conf)
         assert testing.rel_error(out, ref) <= 1e-2 and testing.elementwise_violations(out, ref) == 0
+    # no bounded wait gave up; callers of this entry point read the status without a workspace pointer
+    detail = ctypes.c_int32(-1)
+    assert lib.fp8mm_b200_static_scratch_status(ctypes.byref(detail)) == 0 and detail.value == 0
+    assert lib.fp8mm_b200_last_status(None, ctypes.byref(detail)) == 0 and detail.value == 0
+
+
+def test_static_scratch_allocates_nothing_and_survives_back_to_back_calls():
+    """Free device memory is the same before and after a burst of calls, and two calls with different
+    tile counts queued on one stream without a host synchronisation in between (the second finds the
+    first one's partial tiles and counters in the shared buffer) both give the regular entry point's bits."""
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    probs = []
+    for (m, n, k, impl, conf) in CASES[:2]:
+        A, B, As, Bs = (t.cuda() for t in testing.make_problem(m, n, k, seed=11 + m, mode="normal"))
+        want = engine.launch(A, B, As, Bs, impl, conf)
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        probs.append((A, B, As, Bs, out, want, engine.make_cfg(impl, conf)))
+    A, B, As, Bs, out, _, cfg = probs[0]
+    assert lib.fp8mm_b200_gemm_static_scratch(ctypes.byref(_args(A, B, As, Bs, out)), ctypes.byref(cfg), stream) == 0
+    torch.cuda.synchronize()                                        # first call per device: address look-up done
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(5):
+        for A, B, As, Bs, out, _, cfg in probs:                     # no synchronisation between the calls
+            rc = lib.fp8mm_b200_gemm_static_scratch(ctypes.byref(_args(A, B, As, Bs, out)), ctypes.byref(cfg), stream)
+            assert rc == 0, _lib.strerror(rc)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    for _, _, _, _, out, want, _ in probs:
+        assert torch.equal(out, want)
+    assert lib.fp8mm_b200_static_scratch_status(None) == 0
 
 
 def test_static_scratch_refuses_what_does_not_fit():
