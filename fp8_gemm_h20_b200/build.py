@@ -17,6 +17,7 @@ HEADERS = [PKG / "csrc" / "fp8mm_kernel.cuh", PKG / "csrc" / "fp8mm_kernel_2cta.
            PKG / "csrc" / "ptx_sm100.cuh",
            PKG.parent / "include" / "fp8mm_b200.h"]
 OUT = PKG / "libfp8mm_b200.so"
+TRACE_OUT = PKG / "libfp8mm_b200_trace.so"      # -DFP8MM_TRACE: clock stamps at the role hand-overs (trace.py)
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -24,29 +25,32 @@ NVCC_FLAGS = [
 ]
 
 
-def up_to_date():
-    if not OUT.is_file():
+def up_to_date(out=OUT):
+    if not out.is_file():
         return False
-    t = OUT.stat().st_mtime
+    t = out.stat().st_mtime
     return all(p.stat().st_mtime <= t for p in SOURCES + HEADERS + [Path(__file__)])
 
 
-def build(force=False, verbose=False):
-    if not force and up_to_date():
-        return OUT
+def build(force=False, verbose=False, trace=False):
+    out = TRACE_OUT if trace else OUT
+    if not force and up_to_date(out):
+        return out
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", str(OUT), *map(str, SOURCES)]
+    cmd = [nvcc, *NVCC_FLAGS, *(["-DFP8MM_TRACE"] if trace else []), *(["-Xptxas", "-v"] if verbose else []),
+           "-o", str(out), *map(str, SOURCES)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode:
         raise RuntimeError(f"nvcc failed ({res.returncode}): {' '.join(cmd)}")
-    return OUT
+    return out
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--trace", action="store_true", help="build the instrumented library (libfp8mm_b200_trace.so)")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.trace))

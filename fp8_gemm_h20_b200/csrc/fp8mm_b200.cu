@@ -662,6 +662,10 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
   p.group_m = cfg->group_m;
   p.stages = g.stages;
   p.stg_slabs = g.stg_slabs;
+  p.trace = nullptr;
+#ifdef FP8MM_TRACE
+  if (const char* e = getenv("FP8MM_TRACE_PTR")) p.trace = reinterpret_cast<long long*>(strtoull(e, nullptr, 0));
+#endif
 
   // One CTA per SM unless the shared-memory footprint lets two share an SM.
   int per_sm = (int)((kMaxDynSmem + 1024) / (g.smem + 1024));

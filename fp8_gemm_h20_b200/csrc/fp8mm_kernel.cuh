@@ -47,7 +47,27 @@ struct KParams {
   int group_m;
   int stages;
   int stg_slabs;       // bf16 staging slabs (32 rows x 64 columns) per epilogue warp: 1 or 2
+  long long* trace;    // trace builds only (-DFP8MM_TRACE): clock stamps of CTA 0, else unused
 };
+
+// Trace builds record, for 128 consecutive K blocks of CTA 0 (after 64 blocks of warm-up), the SM
+// clock at the hand-over points of the three roles: 16 slots per K block.  The product build
+// compiles the stamps away.
+//   0 producer saw the ring slot empty      1 producer issued the block's copies
+//   2 issuer saw the slot full              3 issuer saw the TMEM buffer empty
+//   4 issuer issued the block's four MMAs   5 issuer issued both commits
+//   6 promotion (first warp) saw the TMEM buffer full      7 its first loads landed
+//   8 all its loads landed                  9 it released the buffer     10 it finished the block's FMAs
+//  11 promotion (last warp) released the buffer
+#ifdef FP8MM_TRACE
+#define FP8MM_STAMP(slot_, it_)                                                                     \
+  do {                                                                                              \
+    if (blockIdx.x == 0 && p.trace != nullptr && (it_) >= 64u && (it_) < 192u)                      \
+      p.trace[((it_) - 64u) * 16u + (slot_)] = clock64();                                           \
+  } while (0)
+#else
+#define FP8MM_STAMP(slot_, it_) do { } while (0)
+#endif
 
 // Where the bf16 result goes: the caller's C and, for the fused all-gather of the N-sharded
 // layer, the same slice of every peer GPU's buffer (plain peer-to-peer stores; the TMA stores
@@ -335,6 +355,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       const CUtensorMap* col_map = SWAP ? &tm_tok : &tm_wgt;
       int stage = 0;
       uint32_t ph = 0;
+      [[maybe_unused]] uint32_t pit = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
         const UnitCoord c = decode_unit(u, p);
@@ -343,6 +364,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         const int kb0 = c.s * kbn;
         for (int kb = 0; kb < kbn; kb += KG) {
           if (!bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
+          FP8MM_STAMP(0, pit);
           const uint32_t dst = ring + stage * STAGE_BYTES;
           ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
           if constexpr (KG == 1) {
@@ -353,6 +375,8 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
             ptx::tma_load_3d(dst, row_map, bar_full + 8 * stage, 0, row_y, kb0 + kb);
             ptx::tma_load_3d(dst + KG * ROW_BYTES, col_map, bar_full + 8 * stage, 0, col_y, kb0 + kb);
           }
+          FP8MM_STAMP(1, pit);
+          pit += KG;
           if (++stage == stages) { stage = 0; ph ^= 1u; }
         }
       }
@@ -388,9 +412,11 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           }
           const uint32_t buf = it % NBUF, tph = (it / NBUF) & 1u;
           if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
+          FP8MM_STAMP(2, it);
           const uint32_t a_addr = ring + stage * STAGE_BYTES + j * ROW_BYTES;
           const uint64_t a_desc = ptx::smem_desc_k128(a_addr);
           if (!bw.wait(bar_tempty + 8 * buf, tph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
+          FP8MM_STAMP(3, it);
           ptx::tc_fence_after();
           const uint64_t b_desc = ptx::smem_desc_k128(ring + stage * STAGE_BYTES + KG * ROW_BYTES + j * COL_BYTES);
           const uint32_t d_tmem = tmem_base + buf * UMMA_N;
@@ -399,12 +425,14 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
             // 32 fp8 = 32 bytes along K inside the swizzle span: +2 in 16-byte address units.
             ptx::umma_f8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, k);
           }
+          FP8MM_STAMP(4, it);
           ptx::umma_commit(bar_tfull + 8 * buf);   // this K block's partial product is ready
           // A second commit hands the K block's operand tiles back to the producer once these MMAs
           // have retired.  (A commit covers the MMAs of its own thread, i.e. exactly this block.)
           // With two issuing threads there is time for it here, and it takes one barrier operation
           // per K block off the promotion warps, whose pace every other role follows.
           ptx::umma_commit(bar_empty + 8 * stage);
+          FP8MM_STAMP(5, it);
           if (j == KG - 1 && ++stage == stages) { stage = 0; ph ^= 1u; }
         }
       }
@@ -459,6 +487,9 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         const float4* sv = reinterpret_cast<const float4*>(ta + kb * TT + half * CPT);
         const uint32_t tb_idx = buf;
         if (!bw.wait(bar_tfull + 8 * tb_idx, tph, kWaitPromoTmemFull)) { ok = false; break; }
+        [[maybe_unused]] const bool tr_first = leader;
+        [[maybe_unused]] const bool tr_last = threadIdx.x == kProducerThreads + (NPW - 1) * 32;
+        if (tr_first) FP8MM_STAMP(6, it);
         ptx::tc_fence_after();
         const uint32_t taddr = lane_base + buf * UMMA_N;
 // One pair of accumulator columns: the packed FP32 FMA takes half the issue slots of two fmaf and
@@ -488,11 +519,15 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           ptx::tmem_ld<CH>(taddr, d[0]);
           if constexpr (NCH == 2) ptx::tmem_ld<CH>(taddr + CH, d[1]);
           ptx::tmem_wait_ld();
+          if (tr_first) FP8MM_STAMP(8, it);
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * tb_idx);
+          if (tr_first) FP8MM_STAMP(9, it);
+          if (tr_last) FP8MM_STAMP(11, it);
           FP8MM_PROMOTE_CHUNK(d[0], 0);
           if constexpr (NCH == 2) FP8MM_PROMOTE_CHUNK(d[1], 1);
+          if (tr_first) FP8MM_STAMP(10, it);
         } else {
           // 128 columns per thread in two waits instead of four: the chain from "MMAs done" to
           // "buffer handed back" is two TMEM round trips plus 32 FMAs, and it is that chain (with
@@ -501,18 +536,23 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           ptx::tmem_ld<CH>(taddr, d[0]);
           ptx::tmem_ld<CH>(taddr + CH, d[1]);
           ptx::tmem_wait_ld();
+          if (tr_first) FP8MM_STAMP(7, it);
           FP8MM_PROMOTE_CHUNK(d[0], 0);
           ptx::tmem_ld<CH>(taddr + 2 * CH, d[0]);
           FP8MM_PROMOTE_CHUNK(d[1], 1);
           ptx::tmem_ld<CH>(taddr + 3 * CH, d[1]);
           ptx::tmem_wait_ld();
+          if (tr_first) FP8MM_STAMP(8, it);
           // every tcgen05.ld of this warp has completed: hand the buffer back before the last
           // FMAs so the next MMA into it can be issued as early as possible
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * tb_idx);
+          if (tr_first) FP8MM_STAMP(9, it);
+          if (tr_last) FP8MM_STAMP(11, it);
           FP8MM_PROMOTE_CHUNK(d[0], 2);
           FP8MM_PROMOTE_CHUNK(d[1], 3);
+          if (tr_first) FP8MM_STAMP(10, it);
         }
 #undef FP8MM_PROMOTE_CHUNK
 #undef FP8MM_FMA_PAIR

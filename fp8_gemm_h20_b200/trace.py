@@ -1,0 +1,106 @@
+"""Hand-over latencies between the roles of the tile kernel, from clock stamps of one CTA.
+
+    python -m fp8_gemm_h20_b200.build --trace            # libfp8mm_b200_trace.so (-DFP8MM_TRACE)
+    python -m fp8_gemm_h20_b200.trace --mnk 8192,12288,2048 [--impl umma --config '{"BLOCK_W":256}']
+
+The instrumented library stamps the SM clock at twelve points of every K block of CTA 0 (128 blocks
+after 64 of warm-up; csrc/fp8mm_kernel.cuh lists the slots).  From those this tool prints, as medians
+over the window and in SM cycles: the block period, how long each role waits at its barriers, how long
+its own work takes, and the two hand-overs that close the loop around a TMEM accumulator buffer
+(MMAs committed -> promotion warps awake; buffer released -> issuer's next MMAs).  The stamps cost a
+few instructions per block in single threads; the product library is built without them.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+
+SLOTS = 16
+WINDOW = 128
+
+
+def analyse(t, nbuf):
+    """t: WINDOW x SLOTS list of clock values -> dict of medians (cycles)."""
+    def col(s):
+        return [row[s] for row in t]
+
+    def med(xs):
+        xs = [x for x in xs if x is not None]
+        return round(statistics.median(xs), 1) if xs else None
+
+    n = len(t)
+    ok = [i for i in range(n) if all(t[i][s] > 0 for s in (0, 1, 2, 3, 4, 5, 6, 8, 9, 10, 11))]
+    ok = [i for i in ok if i + nbuf < n and (i + nbuf) in set(ok) and i - 1 in set(ok)]
+    out = {"blocks_used": len(ok)}
+    if not ok:
+        return out
+    c = {s: col(s) for s in range(12)}
+    out["block_period"] = med([c[5][i + 1] - c[5][i] for i in ok if i + 1 < n and c[5][i + 1] > 0])
+    # issuer (the thread that owns this block)
+    out["issuer: slot full seen -> TMEM buffer empty seen"] = med([c[3][i] - c[2][i] for i in ok])
+    out["issuer: four MMAs issued"] = med([c[4][i] - c[3][i] for i in ok])
+    out["issuer: two commits issued"] = med([c[5][i] - c[4][i] for i in ok])
+    # promotion
+    out["promotion: previous block done -> buffer full seen (idle)"] = med([c[6][i] - c[10][i - 1] for i in ok])
+    out["promotion: buffer full seen -> first loads landed"] = med([c[7][i] - c[6][i] for i in ok if c[7][i] > 0])
+    out["promotion: buffer full seen -> all loads landed"] = med([c[8][i] - c[6][i] for i in ok])
+    out["promotion: all loads landed -> buffer released (fence, warp sync, arrive)"] = med([c[9][i] - c[8][i] for i in ok])
+    out["promotion: buffer released -> block's FMAs done"] = med([c[10][i] - c[9][i] for i in ok])
+    out["promotion: first warp's release -> last warp's release"] = med([c[11][i] - c[9][i] for i in ok])
+    # hand-overs
+    out["hand-over: MMAs issued (before commit) -> promotion awake"] = med([c[6][i] - c[4][i] for i in ok])
+    out["hand-over: last release -> issuer sees the buffer empty (next use of the buffer)"] = med(
+        [c[3][i + nbuf] - max(c[9][i], c[11][i]) for i in ok])
+    out["buffer cycle: MMAs issued -> MMAs of the next use issued"] = med([c[4][i + nbuf] - c[4][i] for i in ok])
+    # producer
+    out["producer: slot empty seen -> copies issued"] = med([c[1][i] - c[0][i] for i in ok])
+    out["producer: copies issued -> issuer sees the slot full"] = med([c[2][i] - c[1][i] for i in ok])
+    return out
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--mnk", default="8192,12288,2048")
+    ap.add_argument("--impl", default="umma")
+    ap.add_argument("--config", type=json.loads, default={"BLOCK_W": 256, "NUM_STAGES": 4})
+    ap.add_argument("--json", help="also write the raw stamps and the table to this file")
+    a = ap.parse_args(argv)
+
+    from pathlib import Path
+    lib = Path(__file__).with_name("libfp8mm_b200_trace.so")
+    if not lib.is_file():
+        raise SystemExit(f"{lib} missing: python -m fp8_gemm_h20_b200.build --trace")
+    os.environ["FP8MM_LIB"] = str(lib)
+    import torch
+    from . import engine, testing
+    m, n, k = (int(x) for x in a.mnk.split(","))
+    buf = torch.zeros(WINDOW * SLOTS, dtype=torch.int64, device="cuda")
+    os.environ["FP8MM_TRACE_PTR"] = hex(buf.data_ptr())
+    A, B, As, Bs = (x.cuda() for x in testing.make_problem(m, n, k, seed=m + n + k))
+    for _ in range(3):
+        buf.zero_()
+        engine.launch(A, B, As, Bs, a.impl, a.config)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    engine.launch(A, B, As, Bs, a.impl, a.config)
+    e1.record()
+    torch.cuda.synchronize()
+    t = buf.view(WINDOW, SLOTS).cpu().tolist()
+    bw = int(a.config.get("BLOCK_W", 256)) if a.impl == "umma" else int(a.config.get("BLOCK_T", 16))
+    nbuf = 2 if bw == 256 else (4 if bw >= 64 else 8)
+    table = analyse(t, nbuf)
+    table["kernel_us_with_stamps"] = round(e0.elapsed_time(e1) * 1e3, 1)
+    print(json.dumps({"M": m, "N": n, "K": k, "impl": a.impl, "config": a.config, "tmem_buffers": nbuf}))
+    for key, v in table.items():
+        print(f"  {key:82s} {v}")
+    if a.json:
+        with open(a.json, "w") as f:
+            json.dump({"table": table, "stamps": t}, f)
+    assert engine.device_status() == (0, 0)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
