@@ -32,13 +32,17 @@ def up_to_date(out=OUT):
     return all(p.stat().st_mtime <= t for p in SOURCES + HEADERS + [Path(__file__)])
 
 
-def build(force=False, verbose=False, trace=False):
+def build(force=False, verbose=False, trace=False, defines=()):
+    """defines: extra -D macros for the trace library, e.g. FP8MM_KNOBS=1 (no tcgen05.ld), =2 (no operand
+    copies), =4 (no promotion FMAs), FP8MM_SPIN_MASK=1|2 (no suspend hint on the TMEM-buffer waits)."""
     out = TRACE_OUT if trace else OUT
-    if not force and up_to_date(out):
+    if defines and not trace:
+        raise ValueError("extra defines are for the trace library only")
+    if not force and not defines and up_to_date(out):
         return out
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc, *NVCC_FLAGS, *(["-DFP8MM_TRACE"] if trace else []), *(["-Xptxas", "-v"] if verbose else []),
-           "-o", str(out), *map(str, SOURCES)]
+    cmd = [nvcc, *NVCC_FLAGS, *(["-DFP8MM_TRACE"] if trace else []), *[f"-D{d}" for d in defines],
+           *(["-Xptxas", "-v"] if verbose else []), "-o", str(out), *map(str, SOURCES)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode:
         sys.stderr.write(res.stdout + res.stderr)
@@ -52,5 +56,7 @@ if __name__ == "__main__":
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--trace", action="store_true", help="build the instrumented library (libfp8mm_b200_trace.so)")
+    ap.add_argument("-D", dest="defines", action="append", default=[], metavar="MACRO[=VALUE]",
+                    help="with --trace: extra macro, e.g. -D FP8MM_KNOBS=1")
     a = ap.parse_args()
-    print(build(a.force, a.verbose, a.trace))
+    print(build(a.force, a.verbose, a.trace, a.defines))

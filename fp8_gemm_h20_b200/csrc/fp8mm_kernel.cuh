@@ -59,6 +59,18 @@ struct KParams {
 //   6 promotion (first warp) saw the TMEM buffer full      7 its first loads landed
 //   8 all its loads landed                  9 it released the buffer     10 it finished the block's FMAs
 //  11 promotion (last warp) released the buffer
+// Which waits poll without a suspend hint: bit 0 the promotion warps' wait for a full TMEM buffer,
+// bit 1 the MMA issuers' wait for an empty one (the two waits on the loop around a TMEM buffer).
+#ifndef FP8MM_SPIN_MASK
+#define FP8MM_SPIN_MASK 0
+#endif
+// Trace builds can also switch parts of the work off (FP8MM_KNOBS: 1 no tcgen05.ld, 2 no operand
+// copies, 4 no promotion FMAs) to see what the remaining parts then cost; results are garbage.
+#if defined(FP8MM_TRACE) && defined(FP8MM_KNOBS)
+#define FP8MM_KNOB(bit_) ((FP8MM_KNOBS & (bit_)) != 0)
+#else
+#define FP8MM_KNOB(bit_) false
+#endif
 #ifdef FP8MM_TRACE
 #define FP8MM_STAMP(slot_, it_)                                                                     \
   do {                                                                                              \
@@ -110,12 +122,13 @@ struct BoundedWait {
   // Wait for the phase with the given parity.  Gives up after limit_ns (or as soon as
   // another role has given up), records why, and returns false; the caller then leaves
   // its loop so that the CTA can free its TMEM and exit.
+  template <bool SPIN = false>
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, int code) const {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if (SPIN ? ptx::mbar_try_wait_nohint(bar, parity) : ptx::mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     unsigned int it = 0;
     while (true) {
-      if (ptx::mbar_try_wait(bar, parity)) return true;
+      if (SPIN ? ptx::mbar_try_wait_nohint(bar, parity) : ptx::mbar_try_wait(bar, parity)) return true;
       if ((++it & 63u) == 0u) {
         if (*abort) return false;
         unsigned long long now = ptx::globaltimer_ns();
@@ -366,6 +379,13 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           if (!bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
           FP8MM_STAMP(0, pit);
           const uint32_t dst = ring + stage * STAGE_BYTES;
+          if (FP8MM_KNOB(2)) {
+            ptx::mbar_arrive(bar_full + 8 * stage);
+            FP8MM_STAMP(1, pit);
+            pit += KG;
+            if (++stage == stages) { stage = 0; ph ^= 1u; }
+            continue;
+          }
           ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
           if constexpr (KG == 1) {
             ptx::tma_load_2d(dst, row_map, bar_full + 8 * stage, (kb0 + kb) * 128, row_y);
@@ -415,7 +435,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           FP8MM_STAMP(2, it);
           const uint32_t a_addr = ring + stage * STAGE_BYTES + j * ROW_BYTES;
           const uint64_t a_desc = ptx::smem_desc_k128(a_addr);
-          if (!bw.wait(bar_tempty + 8 * buf, tph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
+          if (!bw.wait<(FP8MM_SPIN_MASK & 2) != 0>(bar_tempty + 8 * buf, tph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
           FP8MM_STAMP(3, it);
           ptx::tc_fence_after();
           const uint64_t b_desc = ptx::smem_desc_k128(ring + stage * STAGE_BYTES + KG * ROW_BYTES + j * COL_BYTES);
@@ -486,7 +506,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         if (!SWAP) sc = ta[kb * TT + row] * tb[kb * 2 + (half * CPT) / 128];
         const float4* sv = reinterpret_cast<const float4*>(ta + kb * TT + half * CPT);
         const uint32_t tb_idx = buf;
-        if (!bw.wait(bar_tfull + 8 * tb_idx, tph, kWaitPromoTmemFull)) { ok = false; break; }
+        if (!bw.wait<(FP8MM_SPIN_MASK & 1) != 0>(bar_tfull + 8 * tb_idx, tph, kWaitPromoTmemFull)) { ok = false; break; }
         [[maybe_unused]] const bool tr_first = leader;
         [[maybe_unused]] const bool tr_last = threadIdx.x == kProducerThreads + (NPW - 1) * 32;
         if (tr_first) FP8MM_STAMP(6, it);
@@ -498,6 +518,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
 #define FP8MM_FMA_PAIR(a0_, a1_, d0_, d1_, s0_, s1_) ptx::ffma2(a0_, a1_, d0_, d1_, s0_, s1_)
 #define FP8MM_PROMOTE_CHUNK(dd_, ch_)                                                              \
   do {                                                                                             \
+    if (FP8MM_KNOB(4)) break;                                                                      \
     if (SWAP) {                                                                                    \
       _Pragma("unroll") for (int i_ = 0; i_ < CH; i_ += 4) {                                       \
         const float4 s4_ = sv[((ch_) * CH + i_) >> 2];                                             \
@@ -516,7 +537,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         if constexpr (NCH <= 2) {
           // up to 64 columns per thread: every load in flight at once, one wait, then release
           // the buffer before any FMA
-          ptx::tmem_ld<CH>(taddr, d[0]);
+          if (!FP8MM_KNOB(1)) ptx::tmem_ld<CH>(taddr, d[0]);
           if constexpr (NCH == 2) ptx::tmem_ld<CH>(taddr + CH, d[1]);
           ptx::tmem_wait_ld();
           if (tr_first) FP8MM_STAMP(8, it);
@@ -533,14 +554,14 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           // "buffer handed back" is two TMEM round trips plus 32 FMAs, and it is that chain (with
           // only two 256-column buffers) that paces the kernel, not the FMA or load throughput.
           static_assert(NCH == 4, "two pairs of 32-column loads");
-          ptx::tmem_ld<CH>(taddr, d[0]);
-          ptx::tmem_ld<CH>(taddr + CH, d[1]);
+          if (!FP8MM_KNOB(1)) ptx::tmem_ld<CH>(taddr, d[0]);
+          if (!FP8MM_KNOB(1)) ptx::tmem_ld<CH>(taddr + CH, d[1]);
           ptx::tmem_wait_ld();
           if (tr_first) FP8MM_STAMP(7, it);
           FP8MM_PROMOTE_CHUNK(d[0], 0);
-          ptx::tmem_ld<CH>(taddr + 2 * CH, d[0]);
+          if (!FP8MM_KNOB(1)) ptx::tmem_ld<CH>(taddr + 2 * CH, d[0]);
           FP8MM_PROMOTE_CHUNK(d[1], 1);
-          ptx::tmem_ld<CH>(taddr + 3 * CH, d[1]);
+          if (!FP8MM_KNOB(1)) ptx::tmem_ld<CH>(taddr + 3 * CH, d[1]);
           ptx::tmem_wait_ld();
           if (tr_first) FP8MM_STAMP(8, it);
           // every tcgen05.ld of this warp has completed: hand the buffer back before the last
