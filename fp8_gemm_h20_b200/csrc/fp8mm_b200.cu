@@ -41,7 +41,7 @@ struct Geometry {
   int threads;
   size_t smem;
   int stg_slabs;
-  int kg;              // K blocks per ring slot (1 or 2)
+  int kg;              // K blocks per ring slot (1..8)
   bool gemv;           // CUDA-core decode path: no tiles, no split, no scratch
   size_t counter_bytes, partial_bytes;
 };
@@ -52,7 +52,7 @@ bool cluster_split_allowed();
 int check_cfg(int M, int N, int K, const fp8mm_cfg* c) {
   if (c == nullptr) return FP8MM_E_NULL;
   if (M < 1 || N < 128 || K < 128 || (N % 128) != 0 || (K % 128) != 0) return FP8MM_E_SHAPE;
-  if ((c->flags & ~(FP8MM_FLAG_WORKSPACE_SPLIT | FP8MM_FLAG_K_PAIRS)) != 0) return FP8MM_E_CONFIG;
+  if ((c->flags & ~(FP8MM_FLAG_WORKSPACE_SPLIT | FP8MM_FLAG_K_PAIRS | FP8MM_FLAG_K_GROUP_MASK)) != 0) return FP8MM_E_CONFIG;
   if (c->split < 1 || c->group_m < 1 || c->stages < 0 || c->max_ctas < 0) return FP8MM_E_CONFIG;
   if (c->impl == FP8MM_IMPL_UMMA) {
     if (c->block_t != 128) return FP8MM_E_CONFIG;
@@ -101,13 +101,18 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
                !(c->flags & FP8MM_FLAG_WORKSPACE_SPLIT);
   const int npw = g->umma_n >= 128 ? 8 : 4;
   g->threads = kProducerThreads + npw * 32;
-  // two K blocks per ring slot: narrow swap-AB tiles only, and only if every split has an even count
-  g->kg = ((c->flags & FP8MM_FLAG_K_PAIRS) && g->swap && g->umma_n <= 64 && g->kbn % 2 == 0) ? 2 : 1;
-  const size_t stage_bytes = g->pair ? 2 * 128 * 128 : g->kg * (128 * 128 + (size_t)g->umma_n * 128);
+  // several K blocks per ring slot: narrow swap-AB tiles only, and only if the count divides every
+  // split's K blocks (and two slots of that size fit into shared memory); otherwise one per slot
+  int kg_req = (c->flags & FP8MM_FLAG_K_GROUP_MASK) >> 8;
+  if (kg_req == 0 && (c->flags & FP8MM_FLAG_K_PAIRS)) kg_req = 2;
+  g->kg = (kg_req >= 2 && kg_req <= 8 && g->swap && g->umma_n <= 64 && g->kbn % kg_req == 0) ? kg_req : 1;
+  const size_t block_bytes = g->pair ? 2 * 128 * 128 : (128 * 128 + (size_t)g->umma_n * 128);
   const size_t tab_rows = g->pair ? 128 : g->tt;    // token rows per CTA in the scale table
   const size_t tab_bytes = 2 * (size_t)g->kbn * tab_rows * sizeof(float) + 2 * (size_t)g->kbn * 2 * sizeof(float);
   size_t staging = g->swap ? 0 : (size_t)npw * 4096;   // bf16 output staging for TMA stores
   size_t fixed = 1024 + staging + tab_bytes + sizeof(SharedCtl);
+  if (fixed + 2 * g->kg * block_bytes > kMaxDynSmem) g->kg = 1;     // two slots of that size do not fit
+  const size_t stage_bytes = g->kg * block_bytes;
   if (fixed + 2 * stage_bytes > kMaxDynSmem) return FP8MM_E_CONFIG;
   int stages = c->stages > 0 ? c->stages : (g->pair ? 5 : 4);
   if (stages > kMaxStages) stages = kMaxStages;
@@ -421,7 +426,7 @@ template <int UMMA_N, bool SWAP>
 int launch(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
            const OutTargets& outs, const KParams& p, int grid, cudaStream_t stream) {
   if constexpr (SWAP && UMMA_N <= 64) {
-    if (g.kg == 2) {          // slots 21..29: the two-K-blocks-per-slot variants of the narrow tiles
+    if (g.kg >= 2) {          // slots 21..29: the several-K-blocks-per-slot variants of the narrow tiles
       const int s2 = 21 + 3 * slot;
       if (g.split > 1) {
         if (g.cluster) {
@@ -662,6 +667,7 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
   p.group_m = cfg->group_m;
   p.stages = g.stages;
   p.stg_slabs = g.stg_slabs;
+  p.kg = g.kg;
   p.trace = nullptr;
 #ifdef FP8MM_TRACE
   if (const char* e = getenv("FP8MM_TRACE_PTR")) p.trace = reinterpret_cast<long long*>(strtoull(e, nullptr, 0));

@@ -47,6 +47,7 @@ struct KParams {
   int group_m;
   int stages;
   int stg_slabs;       // bf16 staging slabs (32 rows x 64 columns) per epilogue warp: 1 or 2
+  int kg;              // K blocks per ring slot (1..8); > 1 only in the KG = 2 kernel variants
   long long* trace;    // trace builds only (-DFP8MM_TRACE): clock stamps of CTA 0, else unused
 };
 
@@ -71,15 +72,30 @@ struct KParams {
 #else
 #define FP8MM_KNOB(bit_) false
 #endif
+//  12 kernel entry   13 prologue done (barriers, TMEM, CTA sync)   14 previous grid's results visible
+//  15 promotion leader done with the CTA's last unit (its output stored)      (12..15: row 0 only)
+// FP8MM_TRACE_FROM (default 64) is the first K block recorded; 0 records a short call from its start.
+#ifndef FP8MM_TRACE_FROM
+#define FP8MM_TRACE_FROM 64u
+#endif
 #ifdef FP8MM_TRACE
 #define FP8MM_STAMP(slot_, it_)                                                                     \
   do {                                                                                              \
-    if (blockIdx.x == 0 && p.trace != nullptr && (it_) >= 64u && (it_) < 192u)                      \
-      p.trace[((it_) - 64u) * 16u + (slot_)] = clock64();                                           \
+    if (blockIdx.x == 0 && p.trace != nullptr && (it_) >= FP8MM_TRACE_FROM &&                       \
+        (it_) < FP8MM_TRACE_FROM + 128u)                                                            \
+      p.trace[((it_) - FP8MM_TRACE_FROM) * 16u + (slot_)] = clock64();                              \
+  } while (0)
+#define FP8MM_STAMP0(slot_)                                                                         \
+  do {                                                                                              \
+    if (blockIdx.x == 0 && p.trace != nullptr) p.trace[(slot_)] = clock64();                        \
   } while (0)
 #else
 #define FP8MM_STAMP(slot_, it_) do { } while (0)
+#define FP8MM_STAMP0(slot_) do { } while (0)
 #endif
+// start-up stamps of the roles, in rows 1..3 of the record (slots 12..15 there are otherwise unused):
+//  16+12 producer entered   16+13 producer decoded its first unit   16+14 issuer (warp 1) entered
+//  16+15 promotion entered  32+12 promotion staged the first unit's scales   32+13 ... saw them complete
 
 // Where the bf16 result goes: the caller's C and, for the fused all-gather of the N-sharded
 // layer, the same slice of every peer GPU's buffer (plain peer-to-peer stores; the TMA stores
@@ -122,13 +138,18 @@ struct BoundedWait {
   // Wait for the phase with the given parity.  Gives up after limit_ns (or as soon as
   // another role has given up), records why, and returns false; the caller then leaves
   // its loop so that the CTA can free its TMEM and exit.
+  // SPIN: poll without a suspend hint.
   template <bool SPIN = false>
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, int code) const {
-    if (SPIN ? ptx::mbar_try_wait_nohint(bar, parity) : ptx::mbar_try_wait(bar, parity)) return true;
+    auto attempt = [&]() {
+      if constexpr (SPIN) return ptx::mbar_try_wait_nohint(bar, parity);
+      else return ptx::mbar_try_wait(bar, parity);
+    };
+    if (attempt()) return true;
     unsigned long long t0 = 0;
     unsigned int it = 0;
     while (true) {
-      if (SPIN ? ptx::mbar_try_wait_nohint(bar, parity) : ptx::mbar_try_wait(bar, parity)) return true;
+      if (attempt()) return true;
       if ((++it & 63u) == 0u) {
         if (*abort) return false;
         unsigned long long now = ptx::globaltimer_ns();
@@ -273,9 +294,11 @@ struct KernelTraits {
 // SPLITK: 0 = one CTA owns the whole K range; 1 = fp32 partials through the global workspace;
 // 2 = the `split` CTAs of a tile form a thread-block cluster and reduce through distributed
 //     shared memory (no workspace, no counters).
-// KG = K blocks per ring slot.  With KG = 2 (small-token tiles, an even number of K blocks per
-// unit) one 3-D TMA copy per operand brings two K blocks, which halves what the producer thread
-// issues per K block; the two MMA-issuing threads then each take one block of every slot.
+// KG = 1: one K block per ring slot.  KG = 2: p.kg (2..8) K blocks per ring slot (small-token tiles,
+// K blocks per unit a multiple of p.kg): one 3-D TMA copy per operand brings all of them, which
+// divides what the producer thread issues per K block (its ~300 ns per block pace small-token
+// calls); the two MMA-issuing threads still alternate over the blocks, so each has at least one
+// block in every slot.
 template <int UMMA_N, bool SWAP, int SPLITK, int KG = 1>
 __global__ void __launch_bounds__(KernelTraits<UMMA_N, SWAP>::THREADS, 1)
 fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
@@ -283,8 +306,10 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
                   const __grid_constant__ OutTargets outs, const KParams p) {
   using T = KernelTraits<UMMA_N, SWAP>;
   constexpr int NPW = T::NPW, CPT = T::CPT, CH = T::CH, NCH = T::NCH, TT = T::TT, WT = T::WT;
-  constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES * KG, ROW_BYTES = T::ROW_BYTES, COL_BYTES = T::COL_BYTES;
-  static_assert(KG == 1 || KG == 2, "one or two K blocks per ring slot");
+  static_assert(KG == 1 || KG == 2, "one K block per ring slot, or p.kg of them");
+  const int kgn = KG == 1 ? 1 : p.kg;
+  const uint32_t STAGE_BYTES = T::STAGE_BYTES * (uint32_t)kgn;
+  constexpr uint32_t ROW_BYTES = T::ROW_BYTES, COL_BYTES = T::COL_BYTES;
   constexpr int NBUF = T::NBUF;
   constexpr uint32_t IDESC = ptx::idesc_f8_m128(UMMA_N);
 
@@ -305,6 +330,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) FP8MM_STAMP0(12);
 
   const uint32_t bar_full = ptx::smem_u32(&ctl->full[0]);
   const uint32_t bar_empty = ptx::smem_u32(&ctl->empty[0]);
@@ -345,6 +371,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
+  if (threadIdx.x == 0) FP8MM_STAMP0(13);
 
   // Programmatic dependent launch: everything above touched only this CTA's shared memory and
   // TMEM, so it may overlap the tail of the previous kernel in the stream.  From here on
@@ -352,6 +379,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   // let the next grid in the stream start its own prologue early.
   ptx::grid_dependency_wait();
   ptx::grid_launch_dependents();
+  if (threadIdx.x == 0) FP8MM_STAMP0(14);
 
   BoundedWait bw{&ctl->abort, p.status, p.timeout_ns};
 
@@ -364,26 +392,30 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      FP8MM_STAMP0(16 + 12);
       const CUtensorMap* row_map = SWAP ? &tm_wgt : &tm_tok;
       const CUtensorMap* col_map = SWAP ? &tm_tok : &tm_wgt;
       int stage = 0;
       uint32_t ph = 0;
       [[maybe_unused]] uint32_t pit = 0;
+      bool first_pass = true;
       bool ok = true;
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
         const UnitCoord c = decode_unit(u, p);
         const int row_y = SWAP ? c.wi * 128 : c.ti * 128;
         const int col_y = SWAP ? c.ti * UMMA_N : c.wi * UMMA_N;
         const int kb0 = c.s * kbn;
-        for (int kb = 0; kb < kbn; kb += KG) {
-          if (!bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
+        if (pit == 0) FP8MM_STAMP0(16 + 13);
+        for (int kb = 0; kb < kbn; kb += kgn) {
+          // every slot starts out empty: no wait on the first pass over the ring
+          if (!first_pass && !bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
           FP8MM_STAMP(0, pit);
           const uint32_t dst = ring + stage * STAGE_BYTES;
           if (FP8MM_KNOB(2)) {
             ptx::mbar_arrive(bar_full + 8 * stage);
             FP8MM_STAMP(1, pit);
-            pit += KG;
-            if (++stage == stages) { stage = 0; ph ^= 1u; }
+            pit += kgn;
+            if (++stage == stages) { stage = 0; ph ^= 1u; first_pass = false; }
             continue;
           }
           ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
@@ -391,13 +423,13 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
             ptx::tma_load_2d(dst, row_map, bar_full + 8 * stage, (kb0 + kb) * 128, row_y);
             ptx::tma_load_2d(dst + ROW_BYTES, col_map, bar_full + 8 * stage, (kb0 + kb) * 128, col_y);
           } else {
-            // slot layout: [row tile kb][row tile kb+1][column tile kb][column tile kb+1]
+            // slot layout: [row tile kb] .. [row tile kb+kg-1][column tile kb] .. [column tile kb+kg-1]
             ptx::tma_load_3d(dst, row_map, bar_full + 8 * stage, 0, row_y, kb0 + kb);
-            ptx::tma_load_3d(dst + KG * ROW_BYTES, col_map, bar_full + 8 * stage, 0, col_y, kb0 + kb);
+            ptx::tma_load_3d(dst + kgn * ROW_BYTES, col_map, bar_full + 8 * stage, 0, col_y, kb0 + kb);
           }
           FP8MM_STAMP(1, pit);
-          pit += KG;
-          if (++stage == stages) { stage = 0; ph ^= 1u; }
+          pit += kgn;
+          if (++stage == stages) { stage = 0; ph ^= 1u; first_pass = false; }
         }
       }
     }
@@ -410,24 +442,29 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     // even number of TMEM buffers each thread owns half of them; a tcgen05.commit covers the
     // MMAs of its own thread only, and K blocks are independent (fresh accumulator each).
     if (lane == 0) {
+      if (warp == 1) FP8MM_STAMP0(16 + 14);
       const uint32_t par = warp - 1;
       int stage = 0;
       uint32_t ph = 0, it = 0;
+      uint32_t jn = 0;              // K block inside the ring slot (always 0 with one block per slot)
       bool ok = true;
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
         for (int kb = 0; kb < kbn; ++kb, ++it) {
-          const uint32_t j = KG == 1 ? 0u : (it & 1u);   // which K block of the ring slot
+          const uint32_t j = jn;
+          const bool slot_done = KG == 1 || j + 1 == (uint32_t)kgn;
+          jn = slot_done ? 0u : j + 1;
           if ((it & 1u) != par) {
             // The other thread's block.  With one K block per slot its operands are still awaited
             // here, so that this thread sees every slot of the ring fill in order: a parity wait
             // can only tell the current phase from the one before, and a slot whose previous fill
             // this thread had never seen complete could otherwise read as "already full".  (With
-            // two blocks per slot each thread owns one block of every slot and waits on all.)
+            // several blocks per slot each thread owns at least one block of every slot and waits
+            // on all.)
             if constexpr (KG == 1) {
               if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
               ptx::mbar_arrive(bar_empty + 8 * stage);     // seen: the slot may be refilled
             }
-            if (j == KG - 1 && ++stage == stages) { stage = 0; ph ^= 1u; }
+            if (slot_done && ++stage == stages) { stage = 0; ph ^= 1u; }
             continue;
           }
           const uint32_t buf = it % NBUF, tph = (it / NBUF) & 1u;
@@ -438,7 +475,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           if (!bw.wait<(FP8MM_SPIN_MASK & 2) != 0>(bar_tempty + 8 * buf, tph ^ 1u, kWaitMmaTmemEmpty)) { ok = false; break; }
           FP8MM_STAMP(3, it);
           ptx::tc_fence_after();
-          const uint64_t b_desc = ptx::smem_desc_k128(ring + stage * STAGE_BYTES + KG * ROW_BYTES + j * COL_BYTES);
+          const uint64_t b_desc = ptx::smem_desc_k128(ring + stage * STAGE_BYTES + kgn * ROW_BYTES + j * COL_BYTES);
           const uint32_t d_tmem = tmem_base + buf * UMMA_N;
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k) {
@@ -451,9 +488,11 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           // have retired.  (A commit covers the MMAs of its own thread, i.e. exactly this block.)
           // With two issuing threads there is time for it here, and it takes one barrier operation
           // per K block off the promotion warps, whose pace every other role follows.
-          ptx::umma_commit(bar_empty + 8 * stage);
+          // (Several blocks per slot: the last two blocks of a slot belong to the two threads, and
+          // each thread's commit after its last block covers its earlier blocks of the slot too.)
+          if (KG == 1 || j + 2 >= (uint32_t)kgn) ptx::umma_commit(bar_empty + 8 * stage);
           FP8MM_STAMP(5, it);
-          if (j == KG - 1 && ++stage == stages) { stage = 0; ph ^= 1u; }
+          if (slot_done && ++stage == stages) { stage = 0; ph ^= 1u; }
         }
       }
     }
@@ -483,6 +522,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     const int row = q * 32 + lane;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * CPT;
     const bool leader = threadIdx.x == kProducerThreads;
+    if (leader) FP8MM_STAMP0(16 + 15);
     uint32_t ui = 0, it = 0;
     for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
       const UnitCoord c = decode_unit(u, p);
@@ -491,8 +531,10 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         // first unit of the CTA: all promotion threads stage its scales (one round of loads)
         stage_scales<TT, WT, SWAP, NPW * 32, 8>(threadIdx.x - kProducerThreads, c, p, kbn, tab_a, tab_b);
         ptx::bar_sync(1, NPW * 32);
+        if (leader) FP8MM_STAMP0(32 + 12);
       }
       bool ok = bw.wait(bar_scfull + 8 * t, sph, kWaitPromoScale);
+      if (leader && ui == 0) FP8MM_STAMP0(32 + 13);
       const float* ta = tab_a + t * kbn * TT;
       const float* tb = tab_b + t * kbn * 2;
 
@@ -856,6 +898,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   }
 
   // ---------------------------------------------------------------- teardown
+  if (threadIdx.x == kProducerThreads) FP8MM_STAMP0(15);
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 1) {

@@ -6,17 +6,19 @@
 // from the partner's shared memory.  Every load is an ordinary single-destination
 // cp.async.bulk.tensor issued by the CTA that owns the bytes.
 //
-// Measured on B200 it is correct (bit-equal to the one-CTA 128x256 kernel) but slower,
-// 1.07 against 1.78 PFLOP/s at M=8192, N=12288, K=2048: with per-K-block promotion the pace is
-// set by the commit -> promote -> release round trip between the MMA thread and the promotion
-// warps, and across two SMs that round trip is about twice as long.  The tuning tables do not
-// select it; it stays available as impl "umma_2cta".
+// It is bit-equal to the one-CTA 128x256 kernel.  With per-K-block promotion the pace of both
+// kernels is set by the loop around a TMEM accumulator buffer (MMAs issued -> promotion warps
+// awake -> loads landed -> buffer released -> issuer sees it empty); the pair saves operand
+// traffic but its release crosses from the partner SM to the leader's barrier, which lengthens
+// that loop.  Available as impl "umma_2cta"; the tuner decides where it is used.
 //
 // Roles per CTA are those of fp8mm_umma_kernel (TMA producer, MMA issuer, scale loader, eight
 // promotion/epilogue warps).  Differences:
-//   * only the leader CTA (cluster rank 0) issues MMAs; its `full` barrier collects the
-//     transaction bytes of both CTAs' loads (the partner's TMA signals the leader's barrier);
-//   * one tcgen05.commit per K block is multicast to the `tfull` barrier of both CTAs;
+//   * only the leader CTA (cluster rank 0) issues MMAs (two threads, alternate K blocks); its `full`
+//     barrier collects the transaction bytes of both CTAs' loads (the partner's TMA signals the
+//     leader's barrier);
+//   * two tcgen05.commit per K block, each multicast to both CTAs: `tfull` (the promotion warps)
+//     and `empty` (each CTA's producer gets its ring slot back);
 //   * the leader's `tempty` barrier counts the promotion warps of both CTAs (the partner's
 //     arrive through the cluster shared-memory window);
 //   * TMEM is allocated and freed with the cta_group::2 forms by the same warp of both CTAs;
@@ -159,7 +161,7 @@ fp8mm_umma_2cta_kernel(const __grid_constant__ CUtensorMap tm_tok,
   BoundedWait bw{&ctl->abort, p.status, p.timeout_ns};
 
   if (warp < 4) {
-    ptx::setmaxnreg_dec<64>();
+    ptx::setmaxnreg_dec<56>();
     if (warp == 0) {
       // ---------------------------------------------------------- TMA producer (both CTAs)
       if (lane == 0) {
@@ -202,6 +204,7 @@ fp8mm_umma_2cta_kernel(const __grid_constant__ CUtensorMap tm_tok,
             for (uint32_t k = 0; k < 4; ++k)
               ptx::umma_f8_2cta(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, k);
             ptx::umma_commit_2cta(bar_tfull + 8 * buf, 0x3);   // both CTAs' promotion warps
+            ptx::umma_commit_2cta(bar_empty + 8 * stage, 0x3);  // both CTAs' producers: the slot is free
             if (++stage == stages) { stage = 0; ph ^= 1u; }
           }
         }
@@ -215,35 +218,17 @@ fp8mm_umma_2cta_kernel(const __grid_constant__ CUtensorMap tm_tok,
         const UnitCoord c = decode_unit(u, p);
         const uint32_t t = ui & 1u, tph = (ui >> 1) & 1u;
         if (!bw.wait(bar_scempty + 8 * t, tph ^ 1u, kWaitLoaderEmpty)) break;
-        const int t0 = c.ti * 256 + (int)rank * 128;
-        float* ta = tab_a + t * kbn * TT;
-        float* tb = tab_b + t * kbn * 2;
-        constexpr int U = 8;
-        for (int x = tid; x < TT; x += 64) {
-          const int tok = min(t0 + x, p.M - 1);
-          const float* src = p.As + (long long)tok * p.as_sm;
-          for (int kb = 0; kb < kbn; kb += U) {
-            float v[U];
-#pragma unroll
-            for (int uu = 0; uu < U; ++uu)
-              v[uu] = kb + uu < kbn ? __ldg(src + (long long)(kb + uu) * p.as_sk) : 0.f;
-#pragma unroll
-            for (int uu = 0; uu < U; ++uu)
-              if (kb + uu < kbn) ta[(kb + uu) * TT + x] = v[uu];
-          }
-        }
-        const int nblk_max = p.N / 128 - 1;
-        for (int idx = tid; idx < kbn * 2; idx += 64) {
-          const int kb = idx >> 1, h = idx & 1;
-          const int nb = min(c.wi * 2 + h, nblk_max);
-          tb[idx] = __ldg(p.Bs + (long long)nb * p.bs_sn + (long long)kb * p.bs_sk);
-        }
+        // this CTA's 128 token rows are token tile 2 * ti + rank of the 128-row grid; the first unit's
+        // table is staged by the promotion warps (idle until the first MMAs retire)
+        UnitCoord c2 = c;
+        c2.ti = c.ti * 2 + (int)rank;
+        if (ui > 0) stage_scales<128, 256, false, 64, 4>(tid, c2, p, kbn, tab_a + t * kbn * TT, tab_b + t * kbn * 2);
         ptx::mbar_arrive(bar_scfull + 8 * t);
       }
     }
   } else {
     // ------------------------------------------------------- promotion + epilogue warps
-    ptx::setmaxnreg_inc<216>();
+    ptx::setmaxnreg_inc<224>();
     const int pw = warp - 4;
     const int q = warp & 3;
     const int half = pw >> 2;
@@ -251,10 +236,15 @@ fp8mm_umma_2cta_kernel(const __grid_constant__ CUtensorMap tm_tok,
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * CPT;
     const bool leader = threadIdx.x == kProducerThreads;
     uint32_t ui = 0, it = 0;
-    int pstage = 0;
     for (int u = pair; u < p.num_units; u += pairs, ++ui) {
       const UnitCoord c = decode_unit(u, p);
       const uint32_t t = ui & 1u, sph = (ui >> 1) & 1u;
+      if (ui == 0) {
+        UnitCoord c2 = c;
+        c2.ti = c.ti * 2 + (int)rank;
+        stage_scales<128, 256, false, NPW * 32, 8>(threadIdx.x - kProducerThreads, c2, p, kbn, tab_a, tab_b);
+        ptx::bar_sync(1, NPW * 32);
+      }
       bool ok = bw.wait(bar_scfull + 8 * t, sph, kWaitPromoScale);
       const float* ta = tab_a + t * kbn * TT;
       const float* tb = tab_b + t * kbn * 2;
@@ -267,27 +257,29 @@ fp8mm_umma_2cta_kernel(const __grid_constant__ CUtensorMap tm_tok,
         const uint32_t buf = it & 1u, tph = (it >> 1) & 1u;
         const float sc = ta[kb * TT + row] * tb[kb * 2 + half];
         if (!bw.wait(bar_tfull + 8 * buf, tph, kWaitPromoTmemFull)) { ok = false; break; }
-        // the pair's MMAs on this K block have retired: this CTA's ring slot may be refilled
-        if (leader) ptx::mbar_arrive(bar_empty + 8 * pstage);
-        if (++pstage == stages) pstage = 0;
         ptx::tc_fence_after();
         const uint32_t taddr = lane_base + buf * UMMA_N;
+        // 128 columns per thread in two waits; packed FP32 FMAs (same bits as fmaf); the buffer goes
+        // back to the leader as soon as this warp's loads have landed (fp8mm_kernel.cuh has the why)
+#define FP8MM_PAIR_CHUNK(dd_, ch_)                                                                  \
+  _Pragma("unroll") for (int i_ = 0; i_ < CH; i_ += 2)                                              \
+      ptx::ffma2(acc[(ch_) * CH + i_], acc[(ch_) * CH + i_ + 1], dd_[i_], dd_[i_ + 1], sc, sc)
         uint32_t d[2][CH];
+        static_assert(NCH == 4, "two pairs of 32-column loads");
         ptx::tmem_ld<CH>(taddr, d[0]);
-#pragma unroll
-        for (int ch = 0; ch < NCH; ++ch) {
-          ptx::tmem_wait_ld();
-          if (ch + 1 < NCH) {
-            ptx::tmem_ld<CH>(taddr + (ch + 1) * CH, d[(ch + 1) & 1]);
-          } else {
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(lead_tempty + 8 * buf);   // the leader issues the MMAs
-          }
-#pragma unroll
-          for (int i = 0; i < CH; ++i)
-            acc[ch * CH + i] = fmaf(__uint_as_float(d[ch & 1][i]), sc, acc[ch * CH + i]);
-        }
+        ptx::tmem_ld<CH>(taddr + CH, d[1]);
+        ptx::tmem_wait_ld();
+        FP8MM_PAIR_CHUNK(d[0], 0);
+        ptx::tmem_ld<CH>(taddr + 2 * CH, d[0]);
+        FP8MM_PAIR_CHUNK(d[1], 1);
+        ptx::tmem_ld<CH>(taddr + 3 * CH, d[1]);
+        ptx::tmem_wait_ld();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(lead_tempty + 8 * buf);   // the leader issues the MMAs
+        FP8MM_PAIR_CHUNK(d[0], 2);
+        FP8MM_PAIR_CHUNK(d[1], 3);
+#undef FP8MM_PAIR_CHUNK
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_scempty + 8 * t);

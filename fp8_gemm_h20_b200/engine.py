@@ -29,6 +29,13 @@ _MIN_WORKSPACE = 1 << 20          # bytes; grown on demand, never shrunk
 _workspaces = {}                  # (device index, stream handle) -> uint8 tensor
 
 
+def _k_group_flag(kg):
+    """K blocks per ring slot -> cfg.flags bits (2 keeps its historical bit)."""
+    if kg <= 1:
+        return 0
+    return 2 if kg == 2 else (kg & 15) << 8
+
+
 def make_cfg(impl, config):
     """Table entry -> native fp8mm_cfg."""
     impl_id, defaults = KERNELS[impl]
@@ -37,7 +44,7 @@ def make_cfg(impl, config):
     return _lib.Cfg(impl=impl_id, block_t=int(c["BLOCK_T"]), block_w=int(c["BLOCK_W"]),
                     stages=int(c["NUM_STAGES"]), split=int(c["SPLIT"]),
                     group_m=int(c["GROUP_SIZE_M"]), max_ctas=int(c.get("MAX_CTAS", 0)),
-                    flags=(1 if c.get("SPLIT_VIA_WORKSPACE") else 0) | (2 if int(c.get("K_GROUP", 1)) == 2 else 0))
+                    flags=(1 if c.get("SPLIT_VIA_WORKSPACE") else 0) | _k_group_flag(int(c.get("K_GROUP", 1))))
 
 
 def _workspace(torch, device, stream, nbytes):

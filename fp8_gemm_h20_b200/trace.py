@@ -59,12 +59,37 @@ def analyse(t, nbuf):
     return out
 
 
+def timeline(t):
+    """Stamps of a short call (trace window starting at K block 0) as cycles after kernel entry."""
+    t0 = t[0][12]
+    rel = lambda v: (v - t0) if v > 0 else None
+    out = {"prologue done": rel(t[0][13]), "previous grid's results visible": rel(t[0][14]),
+           "producer entered its role": rel(t[1][12]), "producer decoded its first unit": rel(t[1][13]),
+           "issuer entered its role": rel(t[1][14]), "promotion entered its role": rel(t[1][15]),
+           "promotion staged the first unit's scales": rel(t[2][12]),
+           "promotion saw the scales complete": rel(t[2][13])}
+    blocks = [i for i in range(len(t)) if t[i][1] > 0 or t[i][5] > 0 or t[i][6] > 0]   # rows with K-block stamps
+    names = {0: "producer: slot empty seen", 1: "producer: copies issued", 2: "issuer: slot full seen",
+             3: "issuer: TMEM buffer empty seen", 4: "issuer: MMAs issued", 5: "issuer: commits issued",
+             6: "promotion: buffer full seen", 8: "promotion: loads landed", 9: "promotion: buffer released",
+             10: "promotion: block done"}
+    for i in blocks:
+        for s, nm in names.items():
+            if t[i][s] > 0:
+                out[f"K block {i}: {nm}"] = rel(t[i][s])
+    out["promotion leader done with the last unit (output stored)"] = rel(t[0][15])
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--mnk", default="8192,12288,2048")
     ap.add_argument("--impl", default="umma")
     ap.add_argument("--config", type=json.loads, default={"BLOCK_W": 256, "NUM_STAGES": 4})
     ap.add_argument("--json", help="also write the raw stamps and the table to this file")
+    ap.add_argument("--timeline", action="store_true",
+                    help="a short call from its start (library built with -D FP8MM_TRACE_FROM=0u): cycles after "
+                         "kernel entry at which CTA 0 reached each point")
     a = ap.parse_args(argv)
 
     from pathlib import Path
@@ -90,7 +115,7 @@ def main(argv=None):
     t = buf.view(WINDOW, SLOTS).cpu().tolist()
     bw = int(a.config.get("BLOCK_W", 256)) if a.impl == "umma" else int(a.config.get("BLOCK_T", 16))
     nbuf = 2 if bw == 256 else (4 if bw >= 64 else 8)
-    table = analyse(t, nbuf)
+    table = timeline(t) if a.timeline else analyse(t, nbuf)
     table["kernel_us_with_stamps"] = round(e0.elapsed_time(e1) * 1e3, 1)
     print(json.dumps({"M": m, "N": n, "K": k, "impl": a.impl, "config": a.config, "tmem_buffers": nbuf}))
     for key, v in table.items():

@@ -30,6 +30,32 @@ MODES = ("normal", "outlier", "skew", "zero")
 TIMED_MS = (1, 37, 64, 128, 200, 511, 512, 8192)
 
 
+def summary_markdown(report, ms, argv):
+    """The run in a dozen lines: what the reference keeps as experiments/unification/summary.json."""
+    acc = report["accuracy"]
+    worst = max(acc, key=lambda r: r["error"])
+    by_mode = {mode: max(r["error"] for r in acc if r["mode"] == mode) for mode in MODES}
+    shapes = sorted({(r["N"], r["K"]) for r in acc})
+    lines = [f"# Acceptance run: profile `{report['profile']}` on {report['device']}", "",
+             f"Command: `python -m fp8_gemm_h20_b200.validate {' '.join(argv)}`", "",
+             f"* accuracy: **{len(acc)} cases** = {len(shapes)} shapes x {len(ms)} token counts x {len(MODES)} "
+             f"distributions, every output finite and max|C-ref|/max|ref| < 1e-2 against dequantise -> FP32 matmul "
+             f"(TF32 off) on the GPU; status **{report['status']}**",
+             f"* worst error **{report['worst_error']:.3e}** at M={worst['M']}, N={worst['N']}, K={worst['K']}, "
+             f"`{worst['mode']}` (the reference's own runs on H20: 3.797e-3 / 3.810e-3, "
+             "experiments/unification/summary.json there)",
+             "* worst error per distribution: " + ", ".join(f"{m} {e:.3e}" for m, e in by_mode.items()),
+             f"* token counts: {ms}",
+             f"* two-stream CUDA-graph replay (100 interleaved replays per stream): {len(report['graphs'])} kernel "
+             f"paths, worst error {max(max(g['errors']) for g in report['graphs']):.3e}",
+             f"* strided (transposed-contiguous) scales: {len(report['strided_scales'])} paths, worst error "
+             f"{max(r['error'] for r in report['strided_scales']):.3e}"]
+    if report["timing"]:
+        lines += ["", "| N | K | M | median us |", "|---|---|---|---|"]
+        lines += [f"| {t['N']} | {t['K']} | {t['M']} | {t['median_us']['b200']:.2f} |" for t in report["timing"]]
+    return "\n".join(lines) + "\n"
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--profile", required=True)
@@ -38,6 +64,7 @@ def main(argv=None):
     ap.add_argument("--timing", action="store_true")
     ap.add_argument("--quick", action="store_true", help="five token counts per shape instead of the full list")
     ap.add_argument("--rounds", type=int, default=5)
+    ap.add_argument("--summary-md", help="also write a short markdown summary of the run to this path")
     a = ap.parse_args(argv)
 
     import torch
@@ -130,6 +157,8 @@ def main(argv=None):
     report["status"] = "passed"
     report["worst_error"] = max(r["error"] for r in report["accuracy"])
     Path(a.output).write_text(json.dumps(report, indent=2) + "\n")
+    if a.summary_md:
+        Path(a.summary_md).write_text(summary_markdown(report, ms, argv if argv is not None else sys.argv[1:]))
     print("PASS", a.profile, len(report["accuracy"]), report["worst_error"], flush=True)
     return 0
 

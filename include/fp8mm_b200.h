@@ -55,6 +55,11 @@ extern "C" {
  * (swap-AB tiles of 16..64 tokens; needs an even number of K blocks per split, otherwise ignored).
  * Halves the per-K-block work of the single TMA-issuing thread, which paces small-M calls. */
 #define FP8MM_FLAG_K_PAIRS 2
+/* cfg.flags bits 8..11: K blocks per ring slot, 2..8 (table key K_GROUP); generalises FP8MM_FLAG_K_PAIRS.
+ * Needs the count to divide the K blocks of every split and two such slots to fit in shared
+ * memory, otherwise ignored.  The result bits do not depend on it. */
+#define FP8MM_FLAG_K_GROUP(n) (((n) & 15) << 8)
+#define FP8MM_FLAG_K_GROUP_MASK 0xF00
 
 /*
  * Operands.  Strides are in ELEMENTS and are exactly the values the reference
