@@ -96,6 +96,8 @@ struct KParams {
 // start-up stamps of the roles, in rows 1..3 of the record (slots 12..15 there are otherwise unused):
 //  16+12 producer entered   16+13 producer decoded its first unit   16+14 issuer (warp 1) entered
 //  16+15 promotion entered  32+12 promotion staged the first unit's scales   32+13 ... saw them complete
+//  cluster split-K: 32+14 partial tile parked   32+15 CTA in step   48+12 cluster in step
+//                   48+13 this rank's slice reduced and stored (the closing cluster barrier follows)
 
 // Where the bf16 result goes: the caller's C and, for the fused all-gather of the N-sharded
 // layer, the same slice of every peer GPU's buffer (plain peer-to-peer stores; the TMA stores
@@ -791,8 +793,11 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     // Rank r of the cluster reduces the r-th slice of the tile (token columns of a swap-AB tile,
     // token rows of a token-major one) over all ranks in rank order (the same order as the
     // workspace path: bit-identical results) and writes that slice of the output.
+    if (threadIdx.x == kProducerThreads) FP8MM_STAMP0(32 + 14);    // partial tile parked
     __syncthreads();
+    if (threadIdx.x == kProducerThreads) FP8MM_STAMP0(32 + 15);    // CTA in step
     ptx::cluster_sync_all();             // every CTA's partial tile is in its shared memory
+    if (threadIdx.x == kProducerThreads) FP8MM_STAMP0(48 + 12);    // cluster in step
     if (warp >= 4 && blockIdx.x < p.num_units) {
       const UnitCoord c = decode_unit(blockIdx.x, p);
       const int pw = warp - 4;
@@ -894,6 +899,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
         }
       }
     }
+    if (threadIdx.x == kProducerThreads) FP8MM_STAMP0(48 + 13);    // this rank's slice reduced and stored
     ptx::cluster_sync_all();             // no rank reads this CTA's shared memory any more
   }
 

@@ -72,11 +72,20 @@ def timeline(t):
     names = {0: "producer: slot empty seen", 1: "producer: copies issued", 2: "issuer: slot full seen",
              3: "issuer: TMEM buffer empty seen", 4: "issuer: MMAs issued", 5: "issuer: commits issued",
              6: "promotion: buffer full seen", 8: "promotion: loads landed", 9: "promotion: buffer released",
-             10: "promotion: block done"}
+             10: "promotion: block done", 12: "epilogue of the previous unit entered",
+             13: "previous unit converted and staged", 14: "previous unit's stores handed to the TMA unit",
+             15: "this unit's scale table seen"}
     for i in blocks:
         for s, nm in names.items():
+            if s >= 12 and i < 4:
+                continue              # rows 0..3 carry the start-up and reduction stamps there
             if t[i][s] > 0:
                 out[f"K block {i}: {nm}"] = rel(t[i][s])
+    for (r, sl), nm in {(2, 14): "cluster split-K: partial tile parked", (2, 15): "cluster split-K: CTA in step",
+                        (3, 12): "cluster split-K: cluster in step (first barrier passed)",
+                        (3, 13): "cluster split-K: this rank's slice reduced and stored"}.items():
+        if t[r][sl] > 0:
+            out[nm] = rel(t[r][sl])
     out["promotion leader done with the last unit (output stored)"] = rel(t[0][15])
     return out
 
