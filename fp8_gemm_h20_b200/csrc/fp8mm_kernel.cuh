@@ -333,6 +333,17 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   if (threadIdx.x == 0) FP8MM_STAMP0(12);
+  // Coordinates of this CTA's first unit, worked out here so that the kernel-parameter fetches and the
+  // divisions overlap the barrier set-up and the TMEM allocation below instead of standing between
+  // "previous grid done" and the first operand copy (several hundred cycles on every short call).
+  // (Not in the 256-column kernels: their promotion loop has no register to spare, and a unit there
+  // lasts tens of microseconds.)
+  constexpr bool HOIST = UMMA_N < 256;
+  UnitCoord c_first = {0, 0, 0, 0};
+  if constexpr (HOIST) {
+    c_first = decode_unit(blockIdx.x, p);
+    asm volatile("" ::"r"(c_first.tile), "r"(c_first.ti), "r"(c_first.wi), "r"(c_first.s));
+  }
 
   const uint32_t bar_full = ptx::smem_u32(&ctl->full[0]);
   const uint32_t bar_empty = ptx::smem_u32(&ctl->empty[0]);
@@ -403,7 +414,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       bool first_pass = true;
       bool ok = true;
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
-        const UnitCoord c = decode_unit(u, p);
+        const UnitCoord c = (HOIST && u == (int)blockIdx.x) ? c_first : decode_unit(u, p);
         const int row_y = SWAP ? c.wi * 128 : c.ti * 128;
         const int col_y = SWAP ? c.ti * UMMA_N : c.wi * UMMA_N;
         const int kb0 = c.s * kbn;
@@ -508,7 +519,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     const int tid = threadIdx.x - 96;     // warp 3
     uint32_t ui = 0;
     for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
-      const UnitCoord c = decode_unit(u, p);
+      const UnitCoord c = (HOIST && ui == 0) ? c_first : decode_unit(u, p);
       const uint32_t t = ui & 1u, tph = (ui >> 1) & 1u;
       if (!bw.wait(bar_scempty + 8 * t, tph ^ 1u, kWaitLoaderEmpty)) break;
       if (ui > 0) stage_scales<TT, WT, SWAP, 32, 16>(tid, c, p, kbn, tab_a + t * kbn * TT, tab_b + t * kbn * 2);
@@ -527,7 +538,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     if (leader) FP8MM_STAMP0(16 + 15);
     uint32_t ui = 0, it = 0;
     for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
-      const UnitCoord c = decode_unit(u, p);
+      const UnitCoord c = (HOIST && ui == 0) ? c_first : decode_unit(u, p);
       const uint32_t t = ui & 1u, sph = (ui >> 1) & 1u;
       if (ui == 0) {
         // first unit of the CTA: all promotion threads stage its scales (one round of loads)
@@ -799,7 +810,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     ptx::cluster_sync_all();             // every CTA's partial tile is in its shared memory
     if (threadIdx.x == kProducerThreads) FP8MM_STAMP0(48 + 12);    // cluster in step
     if (warp >= 4 && blockIdx.x < p.num_units) {
-      const UnitCoord c = decode_unit(blockIdx.x, p);
+      const UnitCoord c = HOIST ? c_first : decode_unit(blockIdx.x, p);
       const int pw = warp - 4;
       // A rank whose bounded wait gave up has parked nothing: then no rank stores the tile.  The
       // flags travel with the first batch of partial-tile loads (same round trip) and are looked
