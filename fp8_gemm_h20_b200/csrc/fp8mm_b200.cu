@@ -665,6 +665,10 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
   p.w_tiles = g.w_tiles;
   p.num_units = g.tiles * g.split;
   p.group_m = cfg->group_m;
+  p.fd_split = make_fastdiv(g.split);
+  p.fd_group = make_fastdiv(cfg->group_m * g.w_tiles);
+  p.fd_gm = make_fastdiv(cfg->group_m);
+  p.fd_tail = make_fastdiv(g.t_tiles % cfg->group_m);
   p.stages = g.stages;
   p.stg_slabs = g.stg_slabs;
   p.kg = g.kg;

@@ -30,6 +30,34 @@ namespace fp8mm {
 constexpr int kMaxStages = 12;
 constexpr int kProducerThreads = 128;  // warps 0-3
 
+// Division of a non-negative 31-bit number by a divisor that is fixed for the launch: one
+// multiply-high and a shift (mul = ceil(2^(31+L) / d), L = ceil(log2 d), quotient =
+// umulhi(n, mul) >> (L - 1); exact for 0 <= n < 2^31) in place of the ~30 dependent instructions of a
+// run-time integer division.  The unit decode has five of them in a row, and it sits on the path
+// between two units of a persistent CTA and at the head of a one-unit CTA.
+struct FastDiv {
+  unsigned int mul, shr, div;
+};
+inline FastDiv make_fastdiv(int d) {
+  FastDiv f;
+  f.div = static_cast<unsigned int>(d < 1 ? 1 : d);
+  unsigned int L = 0;
+  while ((1ull << L) < f.div) ++L;
+  if (f.div == 1) { f.mul = 0; f.shr = 0; return f; }
+  const unsigned long long pw = 1ull << (31 + L);
+  f.mul = static_cast<unsigned int>((pw + f.div - 1) / f.div);
+  f.shr = L - 1;
+  return f;
+}
+__host__ __device__ __forceinline__ int fastdiv(int n, const FastDiv& f) {
+#ifdef __CUDA_ARCH__
+  const unsigned int q = __umulhi(static_cast<unsigned int>(n), f.mul) >> f.shr;
+#else
+  const unsigned int q = static_cast<unsigned int>((static_cast<unsigned long long>(n) * f.mul) >> 32) >> f.shr;
+#endif
+  return f.div == 1 ? n : static_cast<int>(q);
+}
+
 struct KParams {
   const float* As;
   const float* Bs;
@@ -45,6 +73,7 @@ struct KParams {
   int t_tiles, w_tiles;
   int num_units;       // t_tiles * w_tiles * split
   int group_m;
+  FastDiv fd_split, fd_group, fd_gm, fd_tail;   // split, group_m * w_tiles, group_m, size of a ragged last group
   int stages;
   int stg_slabs;       // bf16 staging slabs (32 rows x 64 columns) per epilogue warp: 1 or 2
   int kg;              // K blocks per ring slot (1..8); > 1 only in the KG = 2 kernel variants
@@ -60,6 +89,11 @@ struct KParams {
 //   6 promotion (first warp) saw the TMEM buffer full      7 its first loads landed
 //   8 all its loads landed                  9 it released the buffer     10 it finished the block's FMAs
 //  11 promotion (last warp) released the buffer
+// and per unit after the CTA's first, in the row of the NEXT unit's first K block (row >= 4):
+//  12 epilogue entered   13 tile converted and staged   14 stores handed to the TMA unit
+//  15 the next unit's scale table seen
+// and in the row after that: 12 staging fenced for the TMA unit   13 warp in step   14 first store
+//  issued   15 the next unit's loop entered
 // Which waits poll without a suspend hint: bit 0 the promotion warps' wait for a full TMEM buffer,
 // bit 1 the MMA issuers' wait for an empty one (the two waits on the loop around a TMEM buffer).
 #ifndef FP8MM_SPIN_MASK
@@ -147,23 +181,26 @@ struct BoundedWait {
       if constexpr (SPIN) return ptx::mbar_try_wait_nohint(bar, parity);
       else return ptx::mbar_try_wait(bar, parity);
     };
-    if (attempt()) return true;
-    unsigned long long t0 = 0;
-    unsigned int it = 0;
-    while (true) {
-      if (attempt()) return true;
-      if ((++it & 63u) == 0u) {
-        if (*abort) return false;
-        unsigned long long now = ptx::globaltimer_ns();
-        if (t0 == 0) {
-          t0 = now;
-        } else if (now - t0 > limit_ns) {
-          *abort = 1;
-          if (status != nullptr) atomicCAS(status, 0, code);
-          return false;
-        }
+    // The slow path is written without a branch out of the polling loop: the loop ends on one
+    // condition only, whether the phase completed or the wait gave up.  With a second way out of the
+    // loop the register allocator spilled accumulators in the 256-wide kernel's promotion loop
+    // (80-120 bytes per thread, 10-13 % of the kernel's time).
+    bool done = attempt();
+    bool failed = false;
+    if (!done) {
+      const unsigned long long t0 = ptx::globaltimer_ns();
+      do {
+        done = attempt();
+        const bool stop = (*abort != 0) | (ptx::globaltimer_ns() - t0 > limit_ns);
+        failed = stop & !done;
+        done |= stop;
+      } while (!done);
+      if (failed && *abort == 0) {
+        *abort = 1;
+        if (status != nullptr) atomicCAS(status, 0, code);
       }
     }
+    return !failed;
   }
 };
 
@@ -176,15 +213,15 @@ struct UnitCoord {
 // share weight tiles in L2 (the GROUP_SIZE_M raster of kernel_v2.py:125-134).
 __device__ __forceinline__ UnitCoord decode_unit(int u, const KParams& p) {
   UnitCoord c;
-  c.s = u % p.split;
-  c.tile = u / p.split;
-  const int per_group = p.group_m * p.w_tiles;
-  const int g = c.tile / per_group;
+  c.tile = fastdiv(u, p.fd_split);
+  c.s = u - c.tile * p.split;
+  const int g = fastdiv(c.tile, p.fd_group);
   const int first_t = g * p.group_m;
-  const int gsz = min(p.t_tiles - first_t, p.group_m);
-  const int r = c.tile - g * per_group;
-  c.ti = first_t + r % gsz;
-  c.wi = r / gsz;
+  const int r = c.tile - g * static_cast<int>(p.fd_group.div);
+  const bool ragged = first_t + p.group_m > p.t_tiles;   // the last group may hold fewer token tiles
+  c.wi = ragged ? fastdiv(r, p.fd_tail) : fastdiv(r, p.fd_gm);
+  const int gsz = ragged ? p.t_tiles - first_t : p.group_m;
+  c.ti = first_t + r - c.wi * gsz;
   return c;
 }
 
@@ -539,6 +576,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
     uint32_t ui = 0, it = 0;
     for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
       const UnitCoord c = (HOIST && ui == 0) ? c_first : decode_unit(u, p);
+      if (leader && ui > 0 && it >= 4) FP8MM_STAMP(15, it + 1);
       const uint32_t t = ui & 1u, sph = (ui >> 1) & 1u;
       if (ui == 0) {
         // first unit of the CTA: all promotion threads stage its scales (one round of loads)
@@ -548,6 +586,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
       }
       bool ok = bw.wait(bar_scfull + 8 * t, sph, kWaitPromoScale);
       if (leader && ui == 0) FP8MM_STAMP0(32 + 13);
+      if (leader && ui > 0 && it >= 4) FP8MM_STAMP(15, it);
       const float* ta = tab_a + t * kbn * TT;
       const float* tb = tab_b + t * kbn * 2;
 
@@ -570,23 +609,24 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
 // One pair of accumulator columns: the packed FP32 FMA takes half the issue slots of two fmaf and
 // gives the same bits.  The promotion warps share their SM sub-partition's issue port with one
 // another and with the service warps, and their FMAs were half of all instructions issued.
-#define FP8MM_FMA_PAIR(a0_, a1_, d0_, d1_, s0_, s1_) ptx::ffma2(a0_, a1_, d0_, d1_, s0_, s1_)
-#define FP8MM_PROMOTE_CHUNK(dd_, ch_)                                                              \
+#define FP8MM_PROMOTE_CHUNK_(FMA_, dd_, ch_)                                                       \
   do {                                                                                             \
-    if (FP8MM_KNOB(4)) break;                                                                      \
     if (SWAP) {                                                                                    \
       _Pragma("unroll") for (int i_ = 0; i_ < CH; i_ += 4) {                                       \
         const float4 s4_ = sv[((ch_) * CH + i_) >> 2];                                             \
-        FP8MM_FMA_PAIR(acc[(ch_) * CH + i_], acc[(ch_) * CH + i_ + 1], dd_[i_], dd_[i_ + 1],       \
-                       s4_.x, s4_.y);                                                              \
-        FP8MM_FMA_PAIR(acc[(ch_) * CH + i_ + 2], acc[(ch_) * CH + i_ + 3], dd_[i_ + 2],            \
-                       dd_[i_ + 3], s4_.z, s4_.w);                                                 \
+        FMA_(acc[(ch_) * CH + i_], acc[(ch_) * CH + i_ + 1], dd_[i_], dd_[i_ + 1], s4_.x, s4_.y);  \
+        FMA_(acc[(ch_) * CH + i_ + 2], acc[(ch_) * CH + i_ + 3], dd_[i_ + 2], dd_[i_ + 3], s4_.z,  \
+             s4_.w);                                                                               \
       }                                                                                            \
     } else {                                                                                       \
       _Pragma("unroll") for (int i_ = 0; i_ < CH; i_ += 2)                                         \
-        FP8MM_FMA_PAIR(acc[(ch_) * CH + i_], acc[(ch_) * CH + i_ + 1], dd_[i_], dd_[i_ + 1], sc,   \
-                       sc);                                                                        \
+        FMA_(acc[(ch_) * CH + i_], acc[(ch_) * CH + i_ + 1], dd_[i_], dd_[i_ + 1], sc, sc);        \
     }                                                                                              \
+  } while (0)
+#define FP8MM_PROMOTE_CHUNK(dd_, ch_)                                                              \
+  do {                                                                                             \
+    if (FP8MM_KNOB(4)) break;                                                                      \
+    FP8MM_PROMOTE_CHUNK_(ptx::ffma2, dd_, ch_);                                                    \
   } while (0)
         uint32_t d[2][CH];
         if constexpr (NCH <= 2) {
@@ -631,12 +671,13 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
           if (tr_first) FP8MM_STAMP(10, it);
         }
 #undef FP8MM_PROMOTE_CHUNK
-#undef FP8MM_FMA_PAIR
+#undef FP8MM_PROMOTE_CHUNK_
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_scempty + 8 * t);
 
       // ------------------------------------------------------------- epilogue
+      if (leader && it >= 4) FP8MM_STAMP(12, it);
       if constexpr (SPLITK == 2) {
         // Cluster split-K: park the fp32 partial in this CTA's own shared memory (the operand ring
         // is idle: this CTA's only unit is finished); the reduction follows the cluster barrier.
@@ -775,6 +816,7 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
             // One issuing lane per (target, slab): a thread pays a few hundred cycles per TMA
             // instruction, and with up to eight targets (fused all-gather) a single lane would
             // spend longer issuing the stores than the tile took to compute.
+            if (leader && sl == SLABS - 1 && it >= 4) FP8MM_STAMP(13, it);
             if (nsl == 1) {
               ptx::fence_proxy_async_smem();
               __syncwarp();
@@ -784,13 +826,17 @@ fp8mm_umma_kernel(const __grid_constant__ CUtensorMap tm_tok,
               }
             } else if (sl == SLABS - 1) {
               ptx::fence_proxy_async_smem();
+              if (leader && it >= 4) FP8MM_STAMP(12, it + 1);
               __syncwarp();
+              if (leader && it >= 4) FP8MM_STAMP(13, it + 1);
               if (lane < SLABS * outs.n) {
                 const int d = lane / SLABS, ls = lane % SLABS;
                 ptx::tma_store_2d(&outs.map[d], stg_addr + ls * 4096, n0 + ls * 64, m0w);
+                if (leader && it >= 4) FP8MM_STAMP(14, it + 1);
                 ptx::bulk_commit_group();
               }
             }
+            if (leader && sl == SLABS - 1 && it >= 4) FP8MM_STAMP(14, it);
           }
         }
       }
