@@ -90,6 +90,46 @@ def timeline(t):
     return out
 
 
+def boundaries(t, kbn, first_block):
+    """Medians (cycles) over the unit boundaries inside the window: what the promotion warps do between
+    the last K block of one unit and the first of the next, and how long the MMA issuers stand meanwhile.
+    Row r of the record is K block first_block + r of the CTA; a unit has kbn blocks."""
+    def med(xs):
+        xs = [x for x in xs if x is not None]
+        return round(statistics.median(xs), 1) if xs else None
+
+    rows = [r for r in range(1, len(t) - 2) if (r + first_block) % kbn == 0 and t[r][12] > 0 and t[r - 1][10] > 0]
+
+    def d(fn):
+        out = []
+        for r in rows:
+            a, b = fn(r)
+            out.append(b - a if a > 0 and b > 0 else None)
+        return med(out)
+
+    out = {"boundaries_used": len(rows)}
+    if not rows:
+        return out
+    out["last block's FMAs issued -> epilogue entered"] = d(lambda r: (t[r - 1][10], t[r][12]))
+    out["tile converted to bf16 and staged in shared memory"] = d(lambda r: (t[r][12], t[r][13]))
+    out["proxy fence"] = d(lambda r: (t[r][13], t[r + 1][12]))
+    out["warp in step"] = d(lambda r: (t[r + 1][12], t[r + 1][13]))
+    out["first TMA store issued"] = d(lambda r: (t[r + 1][13], t[r + 1][14]))
+    out["bulk group committed"] = d(lambda r: (t[r + 1][14], t[r][14]))
+    out["next unit's loop entered (coordinates decoded)"] = d(lambda r: (t[r][14], t[r + 1][15]))
+    out["next unit's scale table seen"] = d(lambda r: (t[r + 1][15], t[r][15]))
+    out["first TMEM buffer of the next unit seen full"] = d(lambda r: (t[r][15], t[r][6]))
+    out["its loads landed and the buffer released"] = d(lambda r: (t[r][6], t[r][9]))
+    out["promotion: release of the last block -> release of the next unit's first block"] = d(
+        lambda r: (t[r - 1][9], t[r][9]))
+    out["issuer: MMAs of the next unit's 2nd block -> of its 3rd block (stands for the TMEM buffer)"] = d(
+        lambda r: (t[r + 1][4], t[r + 2][4]))
+    inner = [t[r + 1][4] - t[r][4] for r in range(1, len(t) - 1)
+             if (r + first_block) % kbn not in (0, 1, 2, kbn - 1) and t[r][4] > 0 and t[r + 1][4] > 0]
+    out["issuer: block period inside a unit"] = med(inner)
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--mnk", default="8192,12288,2048")
@@ -99,6 +139,10 @@ def main(argv=None):
     ap.add_argument("--timeline", action="store_true",
                     help="a short call from its start (library built with -D FP8MM_TRACE_FROM=0u): cycles after "
                          "kernel entry at which CTA 0 reached each point")
+    ap.add_argument("--boundary", action="store_true",
+                    help="medians over the unit boundaries in the window instead of the per-block table")
+    ap.add_argument("--first-block", type=int, default=64,
+                    help="first K block of the record (the library's FP8MM_TRACE_FROM; 64 unless built otherwise)")
     a = ap.parse_args(argv)
 
     from pathlib import Path
@@ -124,7 +168,10 @@ def main(argv=None):
     t = buf.view(WINDOW, SLOTS).cpu().tolist()
     bw = int(a.config.get("BLOCK_W", 256)) if a.impl == "umma" else int(a.config.get("BLOCK_T", 16))
     nbuf = 2 if bw == 256 else (4 if bw >= 64 else 8)
-    table = timeline(t) if a.timeline else analyse(t, nbuf)
+    if a.boundary:
+        table = boundaries(t, (k // 128) // int(a.config.get("SPLIT", 1)), a.first_block)
+    else:
+        table = timeline(t) if a.timeline else analyse(t, nbuf)
     table["kernel_us_with_stamps"] = round(e0.elapsed_time(e1) * 1e3, 1)
     print(json.dumps({"M": m, "N": n, "K": k, "impl": a.impl, "config": a.config, "tmem_buffers": nbuf}))
     for key, v in table.items():
