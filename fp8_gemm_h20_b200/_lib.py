@@ -18,6 +18,7 @@ IMPL_UMMA = 0
 IMPL_UMMA_SWAP = 1
 IMPL_UMMA_2CTA = 2
 IMPL_GEMV = 3
+IMPL_UMMA_MX = 4
 E_DEVICE_TIMEOUT = -8
 E_TOO_LARGE = -9
 

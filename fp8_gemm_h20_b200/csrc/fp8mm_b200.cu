@@ -15,6 +15,7 @@
 #include "fp8mm_kernel.cuh"
 #include "fp8mm_kernel_2cta.cuh"
 #include "fp8mm_gemv.cuh"
+#include "fp8mm_kernel_mx.cuh"
 
 namespace fp8mm {
 namespace {
@@ -43,6 +44,7 @@ struct Geometry {
   int stg_slabs;
   int kg;              // K blocks per ring slot (1..8)
   bool gemv;           // CUDA-core decode path: no tiles, no split, no scratch
+  bool mx;             // UE8M0 scales through the block-scaled MMA: 128 x 256 tiles, no split
   size_t counter_bytes, partial_bytes;
 };
 
@@ -62,6 +64,8 @@ int check_cfg(int M, int N, int K, const fp8mm_cfg* c) {
     if (!is_pow2(c->block_t) || c->block_t < 16 || c->block_t > 256) return FP8MM_E_CONFIG;
   } else if (c->impl == FP8MM_IMPL_UMMA_2CTA) {
     if (c->block_t != 256 || c->block_w != 256) return FP8MM_E_CONFIG;
+  } else if (c->impl == FP8MM_IMPL_UMMA_MX) {
+    if (!((c->block_t == 128 && c->block_w == 256) || (c->block_t == 256 && c->block_w == 224))) return FP8MM_E_CONFIG;
   } else if (c->impl == FP8MM_IMPL_GEMV) {
     if (c->block_w != kGemvRows) return FP8MM_E_CONFIG;
     if (c->block_t != 1 && c->block_t != 2 && c->block_t != 4) return FP8MM_E_CONFIG;
@@ -81,6 +85,34 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   if (g->gemv) {             // one pass over the weights: nothing to legalise, no scratch
     g->split = 1;
     g->kb_total = g->kbn = K / 128;
+    return FP8MM_OK;
+  }
+  if (c->impl == FP8MM_IMPL_UMMA_MX) {
+    g->mx = true;
+    g->tt = c->block_t;
+    g->wt = c->block_w;
+    g->umma_n = g->wt;
+    g->t_tiles = (M + g->tt - 1) / g->tt;
+    g->w_tiles = (N + g->wt - 1) / g->wt;
+    g->tiles = g->t_tiles * g->w_tiles;
+    g->kb_total = g->kbn = K / 128;
+    g->split = 1;
+    g->kg = 1;
+    g->stg_slabs = 2;
+    g->threads = MxTraits::THREADS;
+    const bool wide = g->tt == 256;
+    const size_t stage_bytes = wide ? Mx256Traits::STAGE_BYTES : MxTraits::STAGE_BYTES;
+    const size_t fixed = 1024 + sizeof(MxCtl) +
+                         (wide ? Mx256Traits::STAGING_BYTES + 2 * Mx256Traits::SF_SLOT_BYTES
+                               : MxTraits::STAGING_BYTES + 2 * MxTraits::SF_SLOT_BYTES);
+    int stages = c->stages > 0 ? c->stages : 4;
+    const int fit = (int)((kMaxDynSmem - fixed) / stage_bytes);
+    if (stages > fit) stages = fit;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return FP8MM_E_CONFIG;
+    g->stages = stages;
+    g->smem = fixed + (size_t)stages * stage_bytes;
+    if (g->smem < 200 * 1024) g->smem = 200 * 1024;   // one CTA per SM: the kernel takes all 512 TMEM columns
     return FP8MM_OK;
   }
   g->swap = c->impl == FP8MM_IMPL_UMMA_SWAP;
@@ -254,7 +286,10 @@ struct OutKey {
   const void* ptr;
   int m, n;
   long long ldc;
-  bool operator==(const OutKey& o) const { return ptr == o.ptr && m == o.m && n == o.n && ldc == o.ldc; }
+  int narrow;     // 0: 64-column boxes, 128-byte swizzle; 1: 32-column boxes, 64-byte swizzle
+  bool operator==(const OutKey& o) const {
+    return ptr == o.ptr && m == o.m && n == o.n && ldc == o.ldc && narrow == o.narrow;
+  }
 };
 struct OutKeyHash {
   size_t operator()(const OutKey& k) const {
@@ -262,13 +297,14 @@ struct OutKeyHash {
     h ^= (size_t)k.m * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
     h ^= (size_t)k.n * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
     h ^= (size_t)k.ldc * 0x165667B19E3779F9ull + (h << 6) + (h >> 2);
+    h ^= (size_t)k.narrow * 0x27D4EB2F165667C5ull;
     return h;
   }
 };
 std::unordered_map<OutKey, CUtensorMap, OutKeyHash> g_out_maps;
 
-int make_output_map(void* c, int m, int n, long long ldc, CUtensorMap* out) {
-  const OutKey key{c, m, n, ldc};
+int make_output_map(void* c, int m, int n, long long ldc, CUtensorMap* out, bool narrow = false) {
+  const OutKey key{c, m, n, ldc, narrow ? 1 : 0};
   {
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_out_maps.find(key);
@@ -281,10 +317,10 @@ int make_output_map(void* c, int m, int n, long long ldc, CUtensorMap* out) {
   if (fn == nullptr) return FP8MM_E_DRIVER;
   cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)m};
   cuuint64_t strides[1] = {(cuuint64_t)ldc * 2};
-  cuuint32_t box[2] = {64u, 32u};
+  cuuint32_t box[2] = {narrow ? 32u : 64u, 32u};
   cuuint32_t estr[2] = {1u, 1u};
   const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, narrow ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return FP8MM_E_DRIVER;
   {
@@ -298,7 +334,7 @@ int make_output_map(void* c, int m, int n, long long ldc, CUtensorMap* out) {
 // ----------------------------------------------------------------- launch
 struct DeviceInfo {
   int sms = 0;
-  bool attr_set[40] = {};     // 0..35 tile kernels, 39 CTA-pair kernel
+  bool attr_set[42] = {};     // 0..35 tile kernels, 39 CTA-pair kernel, 40/41 block-scaled (UE8M0) kernels
   // cluster split-K kernels: can a cluster of 2 / 4 / 8 such CTAs be placed at all?  0 = not asked
   // yet, 1 = yes, 2 = no (an SM-limited context, MPS or a green context can say no)
   unsigned char cluster_ok[40][4] = {};
@@ -381,16 +417,17 @@ int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, 
   return e == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
 }
 
-int launch_pair(int dev, const Geometry& g, const CUtensorMap& tm_tok, const CUtensorMap& tm_wgt,
-                const OutTargets& outs, const KParams& p, int grid, cudaStream_t stream) {
-  auto kern = fp8mm_umma_2cta_kernel;
+// The kernels that exist in one form only: the CTA-pair kernel (slot 39) and the block-scaled one (40).
+typedef void (*PlainKernel)(const CUtensorMap, const CUtensorMap, const OutTargets, const KParams);
+int launch_plain(PlainKernel kern, int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok,
+                 const CUtensorMap& tm_wgt, const OutTargets& outs, const KParams& p, int grid, cudaStream_t stream) {
   {
     std::lock_guard<std::mutex> lk(g_mu);
-    if (!g_dev[dev].attr_set[39]) {
+    if (!g_dev[dev].attr_set[slot]) {
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem) !=
           cudaSuccess)
         return FP8MM_E_LAUNCH;
-      g_dev[dev].attr_set[39] = true;
+      g_dev[dev].attr_set[slot] = true;
     }
   }
   cudaLaunchConfig_t lc = {};
@@ -619,7 +656,7 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
   }
 
   CUtensorMap tm_tok, tm_wgt;
-  rc = get_tensor_map(a->A, a->M, a->K, g.swap ? g.umma_n : 128, &tm_tok, g.kg);
+  rc = get_tensor_map(a->A, a->M, a->K, g.swap ? g.umma_n : (g.mx ? g.tt : 128), &tm_tok, g.kg);
   if (rc != FP8MM_OK) return rc;
   rc = get_tensor_map(a->B, a->N, a->K, (g.swap || g.pair) ? 128 : g.umma_n, &tm_wgt, g.kg, true);
   if (rc != FP8MM_OK) return rc;
@@ -633,7 +670,7 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
     if (reinterpret_cast<uintptr_t>(c) & 15) return FP8MM_E_ALIGN;
     outs.ptr[d] = static_cast<__nv_bfloat16*>(c);
     if (!g.swap) {
-      rc = make_output_map(c, a->M, a->N, a->ldc, &outs.map[d]);
+      rc = make_output_map(c, a->M, a->N, a->ldc, &outs.map[d], g.mx && g.tt == 256);
       if (rc != FP8MM_OK) return rc;
     }
   }
@@ -691,7 +728,11 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
     int pairs = g_dev[dev].sms / 2;
     if (cfg->max_ctas > 0 && pairs > cfg->max_ctas / 2) pairs = cfg->max_ctas / 2 > 0 ? cfg->max_ctas / 2 : 1;
     if (pairs > p.num_units) pairs = p.num_units;
-    return launch_pair(dev, g, tm_tok, tm_wgt, outs, p, 2 * pairs, stream);
+    return launch_plain(fp8mm_umma_2cta_kernel, 39, dev, g, tm_tok, tm_wgt, outs, p, 2 * pairs, stream);
+  }
+  if (g.mx) {
+    return g.tt == 256 ? launch_plain(fp8mm_mx256_kernel, 41, dev, g, tm_tok, tm_wgt, outs, p, grid, stream)
+                       : launch_plain(fp8mm_mx_kernel, 40, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
   }
   if (g.swap) {
     switch (g.umma_n) {

@@ -1,0 +1,613 @@
+// Block-scaled FP8 GEMM for power-of-two (UE8M0) scales on the tensor cores' own scaling path.
+//
+//   C[M,N] (bf16) = sum_kb 2^(As[m,kb]-127) * 2^(Bs[n/128,kb]-127) * (A[m, kb] . B[n, kb])
+//
+// with As, Bs given as UE8M0 bytes (the exponent alone), the form DeepSeek-style checkpoints use on
+// Blackwell.  `tcgen05.mma.kind::mxf8f6f4.block_scale` multiplies every 32-deep slice of the dot
+// product by one scale per row of A and one per row of B, read from tensor memory, and accumulates in
+// FP32 in tensor memory over the whole K: no per-K-block trip of the accumulators through registers
+// (the promotion that paces fp8mm_umma_kernel), one accumulator drain per tile.
+//
+// The reference has one scale per 128 of K (kernel_v2.py:77-91); the instruction wants one per 32.
+// The scale operand is a 32-bit word per row holding four bytes, and the instruction descriptor's
+// scale-factor ids pick the byte: so a word holds the scales of FOUR CONSECUTIVE K BLOCKS, and all
+// four MMAs of K block kb use byte kb % 4.  Per four K blocks the scales of a tile are one 512-byte
+// atom for the 128 token rows and two for the 256 weight rows ([32 lanes][4 words]: word c of lane l
+// belongs to row 32 c + l), copied shared memory -> tensor memory by `tcgen05.cp.32x128b.warpx4`.
+//
+// One CTA per SM, 128 x 256 tiles, persistent.  Warps: 0 TMA producer, 1 MMA issuer (one thread: all
+// MMAs of a tile go to the same accumulator), 2 scale loader, 3 idle, 4-11 epilogue (tcgen05.ld of the
+// finished accumulator, bf16, swizzled staging, TMA store).  Tensor memory: columns 0-255 the
+// accumulator, 256-287 two slots of scale words.  The accumulator is handed back to the issuer as soon
+// as every epilogue warp has it in registers.
+#pragma once
+#include "fp8mm_kernel.cuh"
+
+namespace fp8mm {
+namespace ptx {
+
+__device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t tsfa, uint32_t tsfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+      : "memory");
+}
+// 32 rows x 16 bytes of shared memory -> 32 lanes x 4 columns of tensor memory, repeated in all four
+// lane quarters.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// Shared-memory descriptor of one scale atom: 32 rows of 16 bytes back to back = four 8-row core
+// matrices 128 bytes apart, no swizzle.
+__device__ __forceinline__ uint64_t smem_desc_sf(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(16 >> 4) << 16;     // leading byte offset (one 16-byte column only)
+  d |= static_cast<uint64_t>(128 >> 4) << 32;    // stride byte offset between 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;           // descriptor version of sm_100
+  return d;
+}
+// Instruction descriptor of the block-scaled form: e4m3 x e4m3, K-major, UE8M0 scales, M = 128;
+// `sf` = which byte of the scale words both operands use.
+__host__ __device__ constexpr uint32_t idesc_mxf8_m128(uint32_t n, uint32_t sf) {
+  return (sf << 4)               // B scale-factor id
+         | (0u << 7)             // A format e4m3
+         | (0u << 10)            // B format e4m3
+         | ((n >> 3) << 17)      // N / 8
+         | (1u << 23)            // scale format E8M0
+         | ((128u >> 4) << 24)   // M / 16
+         | (sf << 29);           // A scale-factor id
+}
+
+}  // namespace ptx
+
+struct __align__(8) MxCtl {
+  unsigned long long full[kMaxStages];
+  unsigned long long empty[kMaxStages];
+  unsigned long long sffull[2];
+  unsigned long long sfempty[2];
+  unsigned long long accfull;
+  unsigned long long accempty;
+  unsigned int tmem_base;
+  int abort;
+};
+
+// Codes of the waits of this kernel (role * 16 + barrier kind), next to those of fp8mm_umma_kernel.
+enum : int {
+  kWaitMxIssuerScales = 0x23,
+  kWaitMxIssuerAcc = 0x24,
+  kWaitMxLoaderEmpty = 0x33,
+  kWaitMxEpilogueAcc = 0x44,
+};
+
+struct MxTraits {
+  static constexpr int UMMA_N = 256;
+  static constexpr int THREADS = kProducerThreads + 8 * 32;
+  static constexpr uint32_t ROW_BYTES = 128u * 128u;      // 128 token rows of one K block
+  static constexpr uint32_t COL_BYTES = 256u * 128u;      // 256 weight rows
+  static constexpr uint32_t STAGE_BYTES = ROW_BYTES + COL_BYTES;
+  static constexpr uint32_t STAGING_BYTES = 8u * 2u * 4096u;
+  static constexpr uint32_t SF_SLOT_BYTES = 3u * 512u;    // tokens, weight rows 0-127, weight rows 128-255
+  static constexpr uint32_t TMEM_COLS = 512;
+  static constexpr uint32_t SF_COL = 256;                 // first scale column; 16 columns per slot
+};
+
+__global__ void __launch_bounds__(MxTraits::THREADS, 1)
+fp8mm_mx_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_constant__ CUtensorMap tm_wgt,
+                const __grid_constant__ OutTargets outs, const KParams p) {
+  using T = MxTraits;
+  constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES;
+
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  unsigned char* smem = smem_raw + pad;
+  const uint32_t ring = raw_addr + pad;
+
+  const int kbn = p.kb_per_unit;
+  const int stages = p.stages;
+  const uint32_t staging = ring + stages * STAGE_BYTES;
+  unsigned char* staging_ptr = smem + (size_t)stages * STAGE_BYTES;
+  const uint32_t sf_smem = staging + T::STAGING_BYTES;
+  MxCtl* ctl = reinterpret_cast<MxCtl*>(staging_ptr + T::STAGING_BYTES + 2 * T::SF_SLOT_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t bar_full = ptx::smem_u32(&ctl->full[0]);
+  const uint32_t bar_empty = ptx::smem_u32(&ctl->empty[0]);
+  const uint32_t bar_sffull = ptx::smem_u32(&ctl->sffull[0]);
+  const uint32_t bar_sfempty = ptx::smem_u32(&ctl->sfempty[0]);
+  const uint32_t bar_accfull = ptx::smem_u32(&ctl->accfull);
+  const uint32_t bar_accempty = ptx::smem_u32(&ctl->accempty);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(bar_full + 8 * s, 1);
+      ptx::mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(bar_sffull + 8 * s, 32);
+      ptx::mbar_init(bar_sfempty + 8 * s, 1);
+    }
+    ptx::mbar_init(bar_accfull, 1);
+    ptx::mbar_init(bar_accempty, 8);
+    ctl->abort = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tm_tok);
+    ptx::prefetch_tensormap(&tm_wgt);
+    for (int d = 0; d < outs.n; ++d) ptx::prefetch_tensormap(&outs.map[d]);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&ctl->tmem_base), T::TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
+
+  BoundedWait bw{&ctl->abort, p.status, p.timeout_ns};
+  const unsigned char* As8 = reinterpret_cast<const unsigned char*>(p.As);
+  const unsigned char* Bs8 = reinterpret_cast<const unsigned char*>(p.Bs);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t ph = 0;
+      bool first_pass = true, ok = true;
+      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
+        const UnitCoord c = decode_unit(u, p);
+        for (int kb = 0; kb < kbn; ++kb) {
+          if (!first_pass && !bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
+          const uint32_t dst = ring + stage * STAGE_BYTES;
+          ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
+          ptx::tma_load_2d(dst, &tm_tok, bar_full + 8 * stage, kb * 128, c.ti * 128);
+          ptx::tma_load_2d(dst + T::ROW_BYTES, &tm_wgt, bar_full + 8 * stage, kb * 128, c.wi * 256);
+          if (++stage == stages) { stage = 0; ph ^= 1u; first_pass = false; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t ph = 0, ui = 0, gi = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x, ++ui) {
+        // the epilogue warps hold the previous tile in registers: the accumulator may be overwritten
+        if (ui > 0 && !bw.wait(bar_accempty, (ui - 1) & 1u, kWaitMxIssuerAcc)) break;
+        ptx::tc_fence_after();
+        for (int kb = 0; kb < kbn; ++kb) {
+          const uint32_t slot = gi & 1u;
+          const uint32_t tsf = tmem_base + T::SF_COL + slot * 16u;
+          if ((kb & 3) == 0) {
+            if (!bw.wait(bar_sffull + 8 * slot, (gi >> 1) & 1u, kWaitMxIssuerScales)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const uint32_t src = sf_smem + slot * T::SF_SLOT_BYTES;
+            ptx::tmem_cp_32x128b_warpx4(tsf, ptx::smem_desc_sf(src));
+            ptx::tmem_cp_32x128b_warpx4(tsf + 8u, ptx::smem_desc_sf(src + 512u));
+            ptx::tmem_cp_32x128b_warpx4(tsf + 12u, ptx::smem_desc_sf(src + 1024u));
+          }
+          if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t a_addr = ring + stage * STAGE_BYTES;
+          const uint64_t a_desc = ptx::smem_desc_k128(a_addr);
+          const uint64_t b_desc = ptx::smem_desc_k128(a_addr + T::ROW_BYTES);
+          const uint32_t idesc = ptx::idesc_mxf8_m128(T::UMMA_N, static_cast<uint32_t>(kb & 3));
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            ptx::umma_mxf8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, tsf, tsf + 8u,
+                           static_cast<uint32_t>((kb | k) != 0));
+          ptx::umma_commit(bar_empty + 8 * stage);
+          if ((kb & 3) == 3 || kb == kbn - 1) {
+            ptx::umma_commit(bar_sfempty + 8 * slot);   // scale words and their shared-memory atoms are free
+            ++gi;
+          }
+          if (++stage == stages) { stage = 0; ph ^= 1u; }
+        }
+        if (ok) ptx::umma_commit(bar_accfull);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 2) {
+    // ------------------------------------------------------------ scale loader
+    // Per four K blocks: the UE8M0 bytes of the tile's 128 token rows and 2 weight-row blocks, packed
+    // four K blocks to a word, in the [32 lanes][4 words] order the copy to tensor memory expects.
+    uint32_t gi = 0;
+    bool ok = true;
+    const int nblk_max = p.N / 128 - 1;
+    for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
+      const UnitCoord c = decode_unit(u, p);
+      for (int kb0 = 0; kb0 < kbn; kb0 += 4, ++gi) {
+        const uint32_t slot = gi & 1u, use = gi >> 1;
+        if (use > 0 && !bw.wait(bar_sfempty + 8 * slot, (use - 1) & 1u, kWaitMxLoaderEmpty)) { ok = false; break; }
+        uint32_t wa[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int tok = min(c.ti * 128 + q * 32 + lane, p.M - 1);
+          const unsigned char* src = As8 + (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
+          uint32_t w = 0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t b = (kb0 + j < kbn) ? static_cast<uint32_t>(__ldg(src + (long long)j * p.as_sk)) : 127u;
+            w |= b << (8 * j);
+          }
+          wa[q] = w;
+        }
+        uint32_t wb[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int nb = min(c.wi * 2 + h, nblk_max);
+          const unsigned char* src = Bs8 + (long long)nb * p.bs_sn + (long long)kb0 * p.bs_sk;
+          uint32_t w = 0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t b = (kb0 + j < kbn) ? static_cast<uint32_t>(__ldg(src + (long long)j * p.bs_sk)) : 127u;
+            w |= b << (8 * j);
+          }
+          wb[h] = w;
+        }
+        const uint32_t dst = sf_smem + slot * T::SF_SLOT_BYTES + lane * 16u;
+        ptx::sts_v4(dst, wa[0], wa[1], wa[2], wa[3]);
+        ptx::sts_v4(dst + 512u, wb[0], wb[0], wb[0], wb[0]);
+        ptx::sts_v4(dst + 1024u, wb[1], wb[1], wb[1], wb[1]);
+        ptx::fence_proxy_async_smem();
+        ptx::mbar_arrive(bar_sffull + 8 * slot);
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------- epilogue warps
+    const int pw = warp - 4;
+    const int q = warp & 3;      // TMEM lane quarter this warp may read
+    const int half = pw >> 2;    // which 128 columns of the tile
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * 128;
+    unsigned char* stg = staging_ptr + pw * 8192;
+    const uint32_t stg_addr = staging + pw * 8192;
+    uint32_t ui = 0;
+    for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
+      const UnitCoord c = decode_unit(u, p);
+      if (!bw.wait(bar_accfull, ui & 1u, kWaitMxEpilogueAcc)) break;
+      ptx::tc_fence_after();
+      uint32_t d[4][32];
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) ptx::tmem_ld<32>(taddr + ch * 32, d[ch]);
+      ptx::tmem_wait_ld();
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar_accempty);
+      const int m0w = c.ti * 128 + q * 32;
+      const int n0 = c.wi * 256 + half * 128;
+      if (m0w < p.M && n0 < p.N) {
+        if (lane < 2 * kMaxOutTargets) ptx::bulk_wait_read_all();   // the previous tile has left the staging memory
+        __syncwarp();
+#pragma unroll
+        for (int sl = 0; sl < 2; ++sl) {
+#pragma unroll
+          for (int ck = 0; ck < 8; ++ck) {
+            const uint32_t* v = &d[sl * 2 + (ck >> 2)][(ck & 3) * 8];
+            __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(v[0]), __uint_as_float(v[1]));
+            __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(v[2]), __uint_as_float(v[3]));
+            __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(v[4]), __uint_as_float(v[5]));
+            __nv_bfloat162 v3 = __floats2bfloat162_rn(__uint_as_float(v[6]), __uint_as_float(v[7]));
+            uint4 o;
+            o.x = *reinterpret_cast<uint32_t*>(&v0);
+            o.y = *reinterpret_cast<uint32_t*>(&v1);
+            o.z = *reinterpret_cast<uint32_t*>(&v2);
+            o.w = *reinterpret_cast<uint32_t*>(&v3);
+            *reinterpret_cast<uint4*>(stg + sl * 4096 + lane * 128 + ((ck ^ (lane & 7)) << 4)) = o;
+          }
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane < 2 * outs.n) {
+          const int dd = lane >> 1, ls = lane & 1;
+          ptx::tma_store_2d(&outs.map[dd], stg_addr + ls * 4096, n0 + ls * 64, m0w);
+          ptx::bulk_commit_group();
+        }
+      }
+    }
+    if (lane < 2 * kMaxOutTargets) ptx::bulk_wait_all();
+    __syncwarp();
+  }
+
+  // teardown: every role is out of its loop (or has given up); free the tensor memory
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (ctl->abort) __nanosleep(1000000);  // let copies that are still in flight land
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// The same with 256 x 224 tiles: two 128-row accumulators side by side in tensor memory
+// (2 x 224 columns, the scale words in the 64 that remain), each fed by its own MMA-issuing thread
+// from the SAME weight tile in shared memory.  A 128 x 256 tile draws 48 KB of operands per K block
+// through an L2-to-SM path that delivers ~65 bytes per clock, i.e. ~790 cycles for 512 cycles of MMA;
+// this tile draws 60 KB for 896 cycles of MMA, so the tensor pipe, not the delivery, sets the pace.
+// Epilogue warps take all 224 columns of their rows into registers as packed bf16 (112 registers),
+// hand the accumulator back, and then stage and store 32-column pieces while the next tile runs.
+struct Mx256Traits {
+  static constexpr int UMMA_N = 224;
+  static constexpr int THREADS = kProducerThreads + 8 * 32;
+  static constexpr uint32_t ROW_BYTES = 256u * 128u;      // 256 token rows of one K block
+  static constexpr uint32_t COL_BYTES = 224u * 128u;      // 224 weight rows
+  static constexpr uint32_t STAGE_BYTES = ROW_BYTES + COL_BYTES;
+  static constexpr uint32_t STAGING_BYTES = 8u * 2u * 2048u;   // two 32 x 32 bf16 slabs per epilogue warp
+  static constexpr uint32_t SF_SLOT_BYTES = 4u * 512u;    // token rows 0-127, 128-255, weight rows 0-127, 128-223
+  static constexpr uint32_t TMEM_COLS = 512;
+  static constexpr uint32_t SF_COL = 448;                 // 24 columns per slot: per issuer 4 (tokens) + 8 (weights)
+};
+
+__global__ void __launch_bounds__(Mx256Traits::THREADS, 1)
+fp8mm_mx256_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_constant__ CUtensorMap tm_wgt,
+                   const __grid_constant__ OutTargets outs, const KParams p) {
+  using T = Mx256Traits;
+  constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES;
+
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  unsigned char* smem = smem_raw + pad;
+  const uint32_t ring = raw_addr + pad;
+
+  const int kbn = p.kb_per_unit;
+  const int stages = p.stages;
+  const uint32_t staging = ring + stages * STAGE_BYTES;
+  unsigned char* staging_ptr = smem + (size_t)stages * STAGE_BYTES;
+  const uint32_t sf_smem = staging + T::STAGING_BYTES;
+  MxCtl* ctl = reinterpret_cast<MxCtl*>(staging_ptr + T::STAGING_BYTES + 2 * T::SF_SLOT_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t bar_full = ptx::smem_u32(&ctl->full[0]);
+  const uint32_t bar_empty = ptx::smem_u32(&ctl->empty[0]);
+  const uint32_t bar_sffull = ptx::smem_u32(&ctl->sffull[0]);
+  const uint32_t bar_sfempty = ptx::smem_u32(&ctl->sfempty[0]);
+  const uint32_t bar_accfull = ptx::smem_u32(&ctl->accfull);
+  const uint32_t bar_accempty = ptx::smem_u32(&ctl->accempty);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(bar_full + 8 * s, 1);
+      ptx::mbar_init(bar_empty + 8 * s, 2);     // the commits of both issuing threads
+    }
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(bar_sffull + 8 * s, 32);
+      ptx::mbar_init(bar_sfempty + 8 * s, 2);
+    }
+    ptx::mbar_init(bar_accfull, 2);
+    ptx::mbar_init(bar_accempty, 8);
+    ctl->abort = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tm_tok);
+    ptx::prefetch_tensormap(&tm_wgt);
+    for (int d = 0; d < outs.n; ++d) ptx::prefetch_tensormap(&outs.map[d]);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&ctl->tmem_base), T::TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
+
+  BoundedWait bw{&ctl->abort, p.status, p.timeout_ns};
+  const unsigned char* As8 = reinterpret_cast<const unsigned char*>(p.As);
+  const unsigned char* Bs8 = reinterpret_cast<const unsigned char*>(p.Bs);
+
+  if (warp < 4) {
+  ptx::setmaxnreg_dec<56>();
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t ph = 0;
+      bool first_pass = true, ok = true;
+      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
+        const UnitCoord c = decode_unit(u, p);
+        for (int kb = 0; kb < kbn; ++kb) {
+          if (!first_pass && !bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
+          const uint32_t dst = ring + stage * STAGE_BYTES;
+          ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
+          ptx::tma_load_2d(dst, &tm_tok, bar_full + 8 * stage, kb * 128, c.ti * 256);
+          ptx::tma_load_2d(dst + T::ROW_BYTES, &tm_wgt, bar_full + 8 * stage, kb * 128, c.wi * T::UMMA_N);
+          if (++stage == stages) { stage = 0; ph ^= 1u; first_pass = false; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------------------------------------- MMA issuers
+    // Warp 1 owns the accumulator of token rows 0-127, warp 3 that of rows 128-255; they share nothing
+    // but the operand ring (each copies the scale words it needs into its own tensor-memory columns).
+    if (lane == 0) {
+      const uint32_t h = warp == 1 ? 0u : 1u;
+      const uint32_t d_tmem = tmem_base + h * T::UMMA_N;
+      int stage = 0;
+      uint32_t ph = 0, ui = 0, gi = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x, ++ui) {
+        if (ui > 0 && !bw.wait(bar_accempty, (ui - 1) & 1u, kWaitMxIssuerAcc)) break;
+        ptx::tc_fence_after();
+        for (int kb = 0; kb < kbn; ++kb) {
+          const uint32_t slot = gi & 1u;
+          const uint32_t tsf = tmem_base + T::SF_COL + slot * 24u + h * 12u;
+          if ((kb & 3) == 0) {
+            if (!bw.wait(bar_sffull + 8 * slot, (gi >> 1) & 1u, kWaitMxIssuerScales)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const uint32_t src = sf_smem + slot * T::SF_SLOT_BYTES;
+            ptx::tmem_cp_32x128b_warpx4(tsf, ptx::smem_desc_sf(src + h * 512u));
+            ptx::tmem_cp_32x128b_warpx4(tsf + 4u, ptx::smem_desc_sf(src + 1024u));
+            ptx::tmem_cp_32x128b_warpx4(tsf + 8u, ptx::smem_desc_sf(src + 1536u));
+          }
+          if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t a_addr = ring + stage * STAGE_BYTES;
+          const uint64_t a_desc = ptx::smem_desc_k128(a_addr + h * (128u * 128u));
+          const uint64_t b_desc = ptx::smem_desc_k128(a_addr + T::ROW_BYTES);
+          const uint32_t idesc = ptx::idesc_mxf8_m128(T::UMMA_N, static_cast<uint32_t>(kb & 3));
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            ptx::umma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, tsf, tsf + 4u,
+                           static_cast<uint32_t>((kb | k) != 0));
+          ptx::umma_commit(bar_empty + 8 * stage);
+          if ((kb & 3) == 3 || kb == kbn - 1) {
+            ptx::umma_commit(bar_sfempty + 8 * slot);
+            ++gi;
+          }
+          if (++stage == stages) { stage = 0; ph ^= 1u; }
+        }
+        if (ok) ptx::umma_commit(bar_accfull);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ scale loader
+    // Per four K blocks four atoms: token rows 0-127 and 128-255, weight rows 0-127 and 128-223 of the
+    // tile (a 224-row weight tile does not start on a 128-row scale block: the block of every row is
+    // worked out by itself).
+    uint32_t gi = 0;
+    bool ok = true;
+    const int nblk_max = p.N / 128 - 1;
+    const bool quick_a = p.as_sk == 1 && (p.as_sm & 3) == 0 && (reinterpret_cast<unsigned long long>(As8) & 3ull) == 0;
+    for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
+      const UnitCoord c = decode_unit(u, p);
+      for (int kb0 = 0; kb0 < kbn; kb0 += 4, ++gi) {
+        const uint32_t slot = gi & 1u, use = gi >> 1;
+        if (use > 0 && !bw.wait(bar_sfempty + 8 * slot, (use - 1) & 1u, kWaitMxLoaderEmpty)) { ok = false; break; }
+        const bool whole = kb0 + 3 < kbn;
+        uint32_t w[16];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {        // token rows q * 32 + lane
+          const int tok = min(c.ti * 256 + q * 32 + lane, p.M - 1);
+          const unsigned char* src = As8 + (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
+          uint32_t v = 0;
+          if (quick_a && whole) {
+            v = __ldg(reinterpret_cast<const uint32_t*>(src));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              v |= ((kb0 + j < kbn) ? static_cast<uint32_t>(__ldg(src + (long long)j * p.as_sk)) : 127u) << (8 * j);
+          }
+          w[q] = v;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {        // weight rows q * 32 + lane of the tile (those past 223 are unused)
+          const int nb = min((c.wi * T::UMMA_N + q * 32 + lane) >> 7, nblk_max);
+          const unsigned char* src = Bs8 + (long long)nb * p.bs_sn + (long long)kb0 * p.bs_sk;
+          uint32_t v = 0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            v |= ((kb0 + j < kbn) ? static_cast<uint32_t>(__ldg(src + (long long)j * p.bs_sk)) : 127u) << (8 * j);
+          w[8 + q] = v;
+        }
+        const uint32_t dst = sf_smem + slot * T::SF_SLOT_BYTES + lane * 16u;
+#pragma unroll
+        for (int a = 0; a < 4; ++a) ptx::sts_v4(dst + a * 512u, w[4 * a], w[4 * a + 1], w[4 * a + 2], w[4 * a + 3]);
+        ptx::fence_proxy_async_smem();
+        ptx::mbar_arrive(bar_sffull + 8 * slot);
+      }
+    }
+  }
+  } else {
+    // ---------------------------------------------------------- epilogue warps
+    ptx::setmaxnreg_inc<224>();
+    const int pw = warp - 4;
+    const int q = warp & 3;      // TMEM lane quarter this warp may read
+    const int h = pw >> 2;       // which accumulator (token rows 0-127 or 128-255 of the tile)
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + h * T::UMMA_N;
+    unsigned char* stg = staging_ptr + pw * 4096;
+    const uint32_t stg_addr = staging + pw * 4096;
+    uint32_t ui = 0, pieces = 0;   // pieces staged so far: consecutive pieces alternate between the two slabs
+    for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
+      const UnitCoord c = decode_unit(u, p);
+      if (!bw.wait(bar_accfull, ui & 1u, kWaitMxEpilogueAcc)) break;
+      ptx::tc_fence_after();
+      uint32_t pk[112];          // the thread's 224 columns as bf16 pairs
+      {
+        uint32_t d[4][32];
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) ptx::tmem_ld<32>(taddr + ch * 32, d[ch]);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(d[ch][i]), __uint_as_float(d[ch][i + 1]));
+            pk[ch * 16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&v);
+          }
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch) ptx::tmem_ld<32>(taddr + 128 + ch * 32, d[ch]);
+        ptx::tmem_wait_ld();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar_accempty);     // the accumulator may be overwritten
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(d[ch][i]), __uint_as_float(d[ch][i + 1]));
+            pk[64 + ch * 16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&v);
+          }
+      }
+      const int m0w = c.ti * 256 + h * 128 + q * 32;
+      const int n0 = c.wi * T::UMMA_N;
+      if (m0w < p.M) {
+        // seven pieces of 32 columns through two 2 KB slabs (64-byte rows, 16-byte chunks XOR-swizzled
+        // by row pair = the TMA unit's 64-byte swizzle); a slab is rewritten once the store issued
+        // two pieces earlier has read it
+#pragma unroll
+        for (int pc = 0; pc < 7; ++pc, ++pieces) {
+          if (n0 + pc * 32 >= p.N) break;      // past the edge of C: only stored pieces take turns on the slabs
+          if (lane < kMaxOutTargets) ptx::bulk_wait_read_1();
+          __syncwarp();
+          const uint32_t so = (pieces & 1u) * 2048u;
+          unsigned char* slab = stg + so;
+#pragma unroll
+          for (int ck = 0; ck < 4; ++ck) {
+            uint4 o = make_uint4(pk[pc * 16 + ck * 4], pk[pc * 16 + ck * 4 + 1], pk[pc * 16 + ck * 4 + 2],
+                                 pk[pc * 16 + ck * 4 + 3]);
+            *reinterpret_cast<uint4*>(slab + lane * 64 + ((ck ^ ((lane >> 1) & 3)) << 4)) = o;
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane < outs.n) {
+            ptx::tma_store_2d(&outs.map[lane], stg_addr + so, n0 + pc * 32, m0w);
+            ptx::bulk_commit_group();
+          }
+        }
+      }
+    }
+    if (lane < kMaxOutTargets) ptx::bulk_wait_all();
+    __syncwarp();
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (ctl->abort) __nanosleep(1000000);  // let copies that are still in flight land
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
+}  // namespace fp8mm

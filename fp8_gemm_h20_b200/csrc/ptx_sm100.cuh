@@ -18,6 +18,10 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared::cta.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -101,6 +105,10 @@ __device__ __forceinline__ void bulk_commit_group() {
 // All bulk stores of this thread have finished READING shared memory (the source may be reused).
 __device__ __forceinline__ void bulk_wait_read_all() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// ... all but the most recent group of this thread.
+__device__ __forceinline__ void bulk_wait_read_1() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
 }
 // All bulk stores of this thread have completed, their global (possibly peer) writes included.
 __device__ __forceinline__ void bulk_wait_all() {

@@ -23,6 +23,9 @@ KERNELS = {
     # decode: BLOCK_T tokens per warp (1, 2 or 4), eight weight rows per warp step, FP32 FMAs
     "gemv": (_lib.IMPL_GEMV, {"BLOCK_T": 1, "BLOCK_W": 8, "NUM_STAGES": 1, "SPLIT": 1,
                               "GROUP_SIZE_M": 1, "MAX_CTAS": 0}),
+    # power-of-two scales: As, Bs are uint8 UE8M0 exponents, applied by the block-scaled MMA itself
+    "umma_mx": (_lib.IMPL_UMMA_MX, {"BLOCK_T": 128, "BLOCK_W": 256, "NUM_STAGES": 4, "SPLIT": 1,
+                                    "GROUP_SIZE_M": 8, "MAX_CTAS": 0}),
 }
 
 _MIN_WORKSPACE = 1 << 20          # bytes; grown on demand, never shrunk

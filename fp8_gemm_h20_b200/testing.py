@@ -65,6 +65,30 @@ def make_problem(m, n, k, seed=0, mode="cfg0", device="cpu"):
     return tuple(t.to(device) for t in (A, B, As, Bs))
 
 
+def make_problem_ue8m0(m, n, k, seed=0, device="cpu"):
+    """(A, B, As_u8, Bs_u8, As, Bs): the "cfg0" problem quantised with power-of-two scales (each block's
+    scale rounded UP to 2^e, as UE8M0 checkpoints are made); As_u8/Bs_u8 hold e + 127, As/Bs the same
+    scales as float32 for the references."""
+    import torch
+    gen = torch.Generator().manual_seed(int(seed))
+    x = torch.randn(m, k, generator=gen)
+    w = torch.randn(n, k, generator=gen) * 0.02
+    idx = torch.randperm(k, generator=gen)[:max(1, math.ceil(0.01 * k))]
+    x[:, idx] *= 20.0
+    x = x.to(torch.bfloat16).float()
+    xa = x.view(m, k // 128, 128)
+    ea = torch.ceil(torch.log2(xa.abs().amax(-1).clamp_min(1e-10) / FP8_MAX)).clamp(-127, 127)
+    As = torch.exp2(ea)
+    A = (xa / As[..., None]).clamp(-FP8_MAX, FP8_MAX).reshape(m, k).to(torch.float8_e4m3fn)
+    wb = w.view(n // 128, 128, k // 128, 128)
+    eb = torch.ceil(torch.log2(wb.abs().amax((1, 3)).clamp_min(1e-10) / FP8_MAX)).clamp(-127, 127)
+    Bs = torch.exp2(eb)
+    B = (wb / Bs[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).reshape(n, k).to(torch.float8_e4m3fn)
+    As_u8 = (ea + 127).to(torch.uint8)
+    Bs_u8 = (eb + 127).to(torch.uint8)
+    return tuple(t.contiguous().to(device) for t in (A, B, As_u8, Bs_u8, As, Bs))
+
+
 def reference_fp32(A, B, As, Bs):
     """Dequantise, then one FP32 matmul (the reference's accuracy definition,
     scripts/validate.py:32-34).  Returns float32 [M,N] on the inputs' device."""

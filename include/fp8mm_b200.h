@@ -47,6 +47,12 @@ extern "C" {
                                        step; no tensor memory, no barriers, no tensor maps.  Successor of
                                        the reference's smallest tiles (BT=8, BW=16..128, kernel_v2.py:94-291
                                        with the M<=8 entries of configs/122b_tp4.json)               */
+#define FP8MM_IMPL_UMMA_MX     4    /* power-of-two scales applied by the tensor cores themselves
+                                       (tcgen05.mma kind::mxf8f6f4.block_scale): As and Bs point to UE8M0
+                                       BYTES (value 2^(b-127); strides in bytes), 128 x 256 tiles, FP32
+                                       accumulation over the whole K in tensor memory, no split-K.  The
+                                       native form of the reference adapter's DEEPGEMM_SCALE_UE8M0 mode
+                                       (sgl_patch/fp8mm_sglang_patch.py); block_t 128, block_w 256       */
 
 /* cfg.flags: reduce split-K partials through the global workspace even where the cluster
  * (distributed shared memory) reduction is available (splits of 2, 4 and 8). */
