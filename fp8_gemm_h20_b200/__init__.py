@@ -8,4 +8,11 @@ library is loaded on the first `matmul`.
 from .config import available_profiles, select, supports
 from .dispatch import matmul
 
-__all__ = ["matmul", "available_profiles", "select", "supports"]
+
+def matmul_ue8m0(A, B, As, Bs, *, profile="35b_tp1"):
+    """`matmul` for power-of-two (UE8M0) scales given as bytes, packed words or float32 (quant.py)."""
+    from .quant import matmul_ue8m0 as impl
+    return impl(A, B, As, Bs, profile=profile)
+
+
+__all__ = ["matmul", "matmul_ue8m0", "available_profiles", "select", "supports"]

@@ -51,3 +51,70 @@ def expand_ue8m0(scales):
     if rc != 0:
         raise RuntimeError(f"fp8mm_b200_expand_ue8m0 failed: {_lib.strerror(rc)}")
     return out
+
+
+def ue8m0_bytes(scales):
+    """Scales that are powers of two -> their UE8M0 exponent bytes as a uint8 view/tensor [rows, kblocks].
+
+    Accepts uint8 [rows, kblocks] (returned as is), int32 words of four consecutive K blocks
+    [rows, ceil(kblocks/4)] (the packed form DeepGEMM uses on sm_100: reinterpreted, no copy; the row
+    stride must be in whole words), or float32 powers of two (exponent field taken; one small kernel)."""
+    import torch
+    if scales.dtype == torch.uint8:
+        return scales
+    if scales.dtype == torch.int32:
+        if scales.stride(1) != 1:
+            scales = scales.contiguous()
+        return scales.view(torch.uint8)
+    if scales.dtype == torch.float32:
+        return ((scales.contiguous().view(torch.int32) >> 23) & 0xFF).to(torch.uint8)
+    raise ValueError("UE8M0 scales come as uint8 exponents, int32 words of four exponents, or float32 powers of two")
+
+
+MX_MIN_TOKENS = 256       # below this the table-driven kernels on expanded scales are the faster path
+
+
+def _mx_tile(m, n, k=2048, sms=148):
+    """128x256 or 256x224 tiles, by a cost model fitted to measurements on a B200: waves of tiles over
+    the SMs times the time of one tile = K blocks x block period + the accumulator drain
+    (128x256: ~790 cycles per K block + ~1500; 256x224: ~1200 + ~2600 for 1.75 x the work)."""
+    kb = max(1, k // 128)
+
+    def cost(t, w, period, drain):
+        units = -(-m // t) * -(-n // w)
+        return -(-units // sms) * (kb * period + drain)
+    return (256, 224) if cost(256, 224, 1200, 2600) < cost(128, 256, 790, 1500) else (128, 256)
+
+
+def matmul_ue8m0(A, B, As, Bs, *, profile="35b_tp1"):
+    """`matmul` for power-of-two scales: A[M,K], B[N,K] float8_e4m3fn, As[M,K/128] and Bs[N/128,K/128]
+    in any of the forms `ue8m0_bytes` takes -> bfloat16 C[M,N].
+
+    From MX_MIN_TOKENS tokens on the scales stay bytes and the tensor cores apply them
+    (`umma_mx`, tcgen05.mma kind::mxf8f6f4.block_scale: no shape table needed); below that the scales
+    are expanded to float32 and the call goes through `matmul` and the profile's table."""
+    import torch
+    from . import engine
+    from .dispatch import matmul
+    if A.ndim != 2 or B.ndim != 2:
+        raise ValueError("A and B must be rank-2 tensors")
+    m, k = A.shape
+    n, k_b = B.shape
+    if k != k_b or k % 128 != 0 or n % 128 != 0:
+        raise ValueError("A/B dimensions must match and N,K must be multiples of 128")
+    fp8 = torch.float8_e4m3fn
+    if A.dtype != fp8 or B.dtype != fp8:
+        raise ValueError("A and B must be float8_e4m3fn")
+    if not A.is_cuda or B.device != A.device or As.device != A.device or Bs.device != A.device:
+        raise ValueError("All tensors must reside on the same CUDA device")
+    if not (A.is_contiguous() and B.is_contiguous()):
+        raise ValueError("A and B must be contiguous row-major tensors")
+    kb = k // 128
+    with torch.cuda.device(A.device):
+        a8, b8 = ue8m0_bytes(As), ue8m0_bytes(Bs)
+        if a8.shape[0] != m or a8.shape[1] < kb or b8.shape[0] != n // 128 or b8.shape[1] < kb:
+            raise ValueError("Expected As[M,K/128] and Bs[N/128,K/128] (packed words may pad K/128 up to a multiple of 4)")
+        if m >= MX_MIN_TOKENS:
+            bt, bw = _mx_tile(m, n, k)
+            return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": bt, "BLOCK_W": bw})
+        return matmul(A, B, expand_ue8m0(a8)[:, :kb], expand_ue8m0(b8)[:, :kb], profile=profile)

@@ -12,6 +12,8 @@ Environment:
   FP8MM_PROFILE=35b_tp1|122b_tp4   tuning profile (default 35b_tp1)
   FP8MM_HOME=/path/to/this/repo    prepended to sys.path
   FP8MM_DISABLE_DG_PRECOMPILE=1    also skip DeepGEMM's all-M JIT precompile, unused once patched
+  FP8MM_UE8M0_NATIVE=0             with FP8MM_UE8M0=1: always expand the power-of-two scales to float32 instead
+                                   of handing 256 tokens and more to the block-scaled tensor-core kernel
   FP8MM_UE8M0=1                    also engage when SGLang runs with DEEPGEMM_SCALE_UE8M0 (its default
                                    on Blackwell): power-of-two scales are taken as float32, or expanded
                                    from the packed int32 form once per weight; the activation quantiser
@@ -93,6 +95,15 @@ if os.environ.get("FP8MM_ENABLE") == "1":
                     q, s = quantize(input.view(-1, k), block_size[1], column_major_scales=False,
                                     scale_tma_aligned=False, scale_ue8m0=True)
                     if weight_scale.dtype != torch.float32:
+                        from fp8_gemm_h20_b200 import quant
+                        if input.numel() // k >= quant.MX_MIN_TOKENS and os.environ.get("FP8MM_UE8M0_NATIVE", "1") != "0":
+                            # enough tokens for the tensor cores' own block scaling: the packed exponent
+                            # words go to the kernel as they are, the activation scales as exponent bytes
+                            ws = weight_scale if weight_scale.shape[0] == n // 128 else weight_scale[::128]
+                            out = quant.matmul_ue8m0(q, weight, s, ws, profile=profile)
+                            if bias is not None:
+                                out = out + bias
+                            return out.view(*input.shape[:-1], n)
                         weight_scale = weight_scales_f32(weight, weight_scale)
                 else:
                     q, s = quantize(input.view(-1, k), block_size[1], column_major_scales=False,
