@@ -111,8 +111,10 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return FP8MM_E_CONFIG;
     g->stages = stages;
-    g->smem = fixed + (size_t)stages * stage_bytes;
-    if (g->smem < 200 * 1024) g->smem = 200 * 1024;   // one CTA per SM: the kernel takes all 512 TMEM columns
+    // the kernel takes all 512 TMEM columns, so it asks for all of the shared memory too: no other CTA
+    // (of any stream) can then sit on the same SM waiting for tensor memory (the rule the tile kernels
+    // follow: shared-memory share >= TMEM share)
+    g->smem = kMaxDynSmem;
     return FP8MM_OK;
   }
   g->swap = c->impl == FP8MM_IMPL_UMMA_SWAP;
