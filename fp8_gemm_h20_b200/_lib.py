@@ -31,6 +31,7 @@ SYMBOLS = (
     "fp8mm_b200_gemm_bcast",
     "fp8mm_b200_gemm_static_scratch",
     "fp8mm_b200_quantize_act",
+    "fp8mm_b200_quantize_act_ue8m0",
     "fp8mm_b200_expand_ue8m0",
     "fp8mm_b200_static_scratch_bytes",
     "fp8mm_b200_static_scratch_status",
@@ -101,6 +102,8 @@ def load():
                                                 ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                                 ctypes.c_float, ctypes.c_void_p]
         lib.fp8mm_b200_quantize_act.restype = ctypes.c_int
+        lib.fp8mm_b200_quantize_act_ue8m0.argtypes = lib.fp8mm_b200_quantize_act.argtypes
+        lib.fp8mm_b200_quantize_act_ue8m0.restype = ctypes.c_int
         lib.fp8mm_b200_expand_ue8m0.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
                                                 ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p]
         lib.fp8mm_b200_expand_ue8m0.restype = ctypes.c_int

@@ -17,8 +17,12 @@
 
 namespace {
 
+// POW2: the scale is rounded UP to a power of two and stored as its UE8M0 exponent byte (value
+// 2^(b-127)), the form the block-scaled tensor-core kernels take (SGLang's quantiser with
+// scale_ue8m0=True follows the same rule).
+template <bool POW2>
 __global__ void __launch_bounds__(256) quantize_act_kernel(const __nv_bfloat16* __restrict__ x,
-                                                           uint8_t* __restrict__ a, float* __restrict__ as,
+                                                           uint8_t* __restrict__ a, void* __restrict__ as_,
                                                            int M, int K, long long ldx, long long as_sm,
                                                            long long as_sk, float floor_) {
   const int groups_per_row = K >> 7;
@@ -49,7 +53,13 @@ __global__ void __launch_bounds__(256) quantize_act_kernel(const __nv_bfloat16* 
     for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
 #pragma unroll
     for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 16));
-    const float scale = __fdiv_rn(fmaxf(amax, floor_), 448.f);
+    float scale = __fdiv_rn(fmaxf(amax, floor_), 448.f);
+    uint32_t ebyte = 0;
+    if (POW2) {
+      const uint32_t bits = __float_as_uint(scale);          // positive and normal: floor_ > 0
+      ebyte = min(((bits >> 23) & 0xFFu) + ((bits & 0x7FFFFFu) != 0u ? 1u : 0u), 254u);
+      scale = __uint_as_float(ebyte << 23);
+    }
     uint2 packed;
     uint16_t* out16 = reinterpret_cast<uint16_t*>(&packed);
 #pragma unroll
@@ -61,17 +71,21 @@ __global__ void __launch_bounds__(256) quantize_act_kernel(const __nv_bfloat16* 
     }
     if (valid) {
       *reinterpret_cast<uint2*>(a + (long long)m * K + kb * 128 + sub * 8) = packed;
-      if (sub == 0) as[(long long)m * as_sm + (long long)kb * as_sk] = scale;
+      if (sub == 0) {
+        const long long at = (long long)m * as_sm + (long long)kb * as_sk;
+        if (POW2) static_cast<uint8_t*>(as_)[at] = static_cast<uint8_t>(ebyte);
+        else static_cast<float*>(as_)[at] = scale;
+      }
     }
   }
 }
 
 }  // namespace
 
-extern "C" int fp8mm_b200_quantize_act(const void* x_bf16, void* a_e4m3, float* as, int32_t M, int32_t K,
-                                       int64_t ldx, int64_t as_stride_m, int64_t as_stride_k, float floor_,
-                                       void* stream) {
+static int quantize_act(bool pow2, const void* x_bf16, void* a_e4m3, void* as, int32_t M, int32_t K, int64_t ldx,
+                        int64_t as_stride_m, int64_t as_stride_k, float floor_, void* stream) {
   if (x_bf16 == nullptr || a_e4m3 == nullptr || as == nullptr) return FP8MM_E_NULL;
+  if (!(floor_ > 0.f)) return FP8MM_E_CONFIG;
   if (M < 1 || K < 128 || (K % 128) != 0) return FP8MM_E_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(a_e4m3) & 7) || ldx < K ||
       (ldx % 8) != 0)
@@ -84,10 +98,27 @@ extern "C" int fp8mm_b200_quantize_act(const void* x_bf16, void* a_e4m3, float* 
   long long blocks = (groups * 16 + 255) / 256;
   const long long cap = (long long)sms * 8;               // 8 resident CTAs of 256 threads per SM
   if (blocks > cap) blocks = cap;
-  quantize_act_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(a_e4m3), as, M, K, ldx, as_stride_m,
-      as_stride_k, floor_);
+  if (pow2)
+    quantize_act_kernel<true><<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(a_e4m3), as, M, K, ldx, as_stride_m,
+        as_stride_k, floor_);
+  else
+    quantize_act_kernel<false><<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(a_e4m3), as, M, K, ldx, as_stride_m,
+        as_stride_k, floor_);
   return cudaGetLastError() == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
+}
+
+extern "C" int fp8mm_b200_quantize_act(const void* x_bf16, void* a_e4m3, float* as, int32_t M, int32_t K,
+                                       int64_t ldx, int64_t as_stride_m, int64_t as_stride_k, float floor_,
+                                       void* stream) {
+  return quantize_act(false, x_bf16, a_e4m3, as, M, K, ldx, as_stride_m, as_stride_k, floor_, stream);
+}
+
+extern "C" int fp8mm_b200_quantize_act_ue8m0(const void* x_bf16, void* a_e4m3, uint8_t* as_e, int32_t M, int32_t K,
+                                             int64_t ldx, int64_t as_stride_m, int64_t as_stride_k, float floor_,
+                                             void* stream) {
+  return quantize_act(true, x_bf16, a_e4m3, as_e, M, K, ldx, as_stride_m, as_stride_k, floor_, stream);
 }
 
 // ------------------------------------------------------------------ UE8M0 scale expansion

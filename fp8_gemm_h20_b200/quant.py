@@ -6,21 +6,26 @@ float8_e4m3fn contiguous, As [M,K/128] float32 row-major."""
 from . import _lib
 
 
-def quantize_activations(x, floor=1e-10):
-    """x: CUDA bfloat16 [M, K] (K a multiple of 128, unit column stride) -> (A, As)."""
+def quantize_activations(x, floor=1e-10, ue8m0=False):
+    """x: CUDA bfloat16 [M, K] (K a multiple of 128, unit column stride) -> (A, As).
+
+    ue8m0=True rounds every group's scale UP to a power of two and returns As as uint8 exponents
+    (value 2^(b-127)), what `matmul_ue8m0` and the block-scaled kernels take."""
     import torch
     if x.ndim != 2 or x.dtype != torch.bfloat16 or not x.is_cuda or x.stride(1) != 1:
         raise ValueError("x must be a CUDA bfloat16 [M,K] tensor with unit column stride")
     m, k = x.shape
     if k % 128 or m < 1:
         raise ValueError("K must be a multiple of 128 and M >= 1")
+    if not floor > 0:
+        raise ValueError("floor must be positive")
     lib = _lib.load()
     A = torch.empty((m, k), dtype=torch.float8_e4m3fn, device=x.device)
-    As = torch.empty((m, k // 128), dtype=torch.float32, device=x.device)
+    As = torch.empty((m, k // 128), dtype=torch.uint8 if ue8m0 else torch.float32, device=x.device)
+    fn = lib.fp8mm_b200_quantize_act_ue8m0 if ue8m0 else lib.fp8mm_b200_quantize_act
     with torch.cuda.device(x.device):
-        rc = lib.fp8mm_b200_quantize_act(x.data_ptr(), A.data_ptr(), As.data_ptr(), m, k, x.stride(0),
-                                         As.stride(0), As.stride(1), float(floor),
-                                         torch.cuda.current_stream(x.device).cuda_stream)
+        rc = fn(x.data_ptr(), A.data_ptr(), As.data_ptr(), m, k, x.stride(0), As.stride(0), As.stride(1),
+                float(floor), torch.cuda.current_stream(x.device).cuda_stream)
     if rc != 0:
         raise RuntimeError(f"fp8mm_b200_quantize_act failed: {_lib.strerror(rc)}")
     return A, As

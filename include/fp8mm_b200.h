@@ -206,6 +206,14 @@ int fp8mm_b200_quantize_act(const void* x_bf16, void* a_e4m3, float* as, int32_t
                             int64_t ldx, int64_t as_stride_m, int64_t as_stride_k, float floor_,
                             void* stream);
 
+/* The same with power-of-two scales: the scale of a group is rounded UP to 2^e and written as the
+ * UE8M0 byte e + 127 (as_e[M,K/128], strides in bytes), the operand form of FP8MM_IMPL_UMMA_MX.
+ * Stands where the adapter calls the same SGLang function with scale_ue8m0=True
+ * (sgl_patch/fp8mm_sglang_patch.py:53 with DEEPGEMM_SCALE_UE8M0).  floor_ must be > 0. */
+int fp8mm_b200_quantize_act_ue8m0(const void* x_bf16, void* a_e4m3, uint8_t* as_e, int32_t M, int32_t K,
+                                  int64_t ldx, int64_t as_stride_m, int64_t as_stride_k, float floor_,
+                                  void* stream);
+
 /* UE8M0 scales (8-bit exponent, value 2^(e-127): the scale format of Blackwell block-scaled MMA,
  * which SGLang/DeepGEMM switch to on sm_100) -> contiguous fp32 [rows, kblocks], exactly.
  * packed4 = 0: src is bytes, element (r, kb) at src[r*row_stride + kb*col_stride] (strides in bytes).

@@ -98,6 +98,21 @@ def quantize_activations(x, floor=1e-10):
     return e4m3_encode(q).reshape(m, k), scale
 
 
+def quantize_activations_ue8m0(x, floor=1e-10):
+    """The same with power-of-two scales: amax/448 rounded UP to 2^e, returned as the UE8M0 byte e + 127
+    (the rule of SGLang's quantiser under scale_ue8m0=True, which the reference's adapter meets with
+    DEEPGEMM_SCALE_UE8M0, sgl_patch/fp8mm_sglang_patch.py:41).  x [M,K] f32 -> (A bytes, exponents u8)."""
+    x = np.asarray(x, dtype=np.float32)
+    m, k = x.shape
+    g = x.reshape(m, k // 128, 128)
+    scale = (np.maximum(np.abs(g).max(-1), np.float32(floor)) / np.float32(FP8_MAX)).astype(np.float32)
+    mant, exp = np.frexp(scale)                        # scale = mant * 2^exp, mant in [0.5, 1)
+    e = np.where(mant == 0.5, exp - 1, exp).astype(np.int32)     # ceil(log2(scale)), exactly
+    pow2 = np.ldexp(np.float32(1.0), e).astype(np.float32)
+    q = np.clip(g / pow2[..., None], -FP8_MAX, FP8_MAX).astype(np.float32)
+    return e4m3_encode(q).reshape(m, k), np.minimum(e + 127, 254).astype(np.uint8)
+
+
 def quantize_weights(w, floor=1e-10):
     """w [N,K] f32 -> (B bytes [N,K], Bs f32 [N/128,K/128]): amax/448 per 128x128 block
     (scripts/validate.py:27,29; bench.py:19-21)."""
