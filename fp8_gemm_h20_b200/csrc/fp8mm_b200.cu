@@ -65,7 +65,8 @@ int check_cfg(int M, int N, int K, const fp8mm_cfg* c) {
   } else if (c->impl == FP8MM_IMPL_UMMA_2CTA) {
     if (c->block_t != 256 || c->block_w != 256) return FP8MM_E_CONFIG;
   } else if (c->impl == FP8MM_IMPL_UMMA_MX) {
-    if (!((c->block_t == 128 && c->block_w == 256) || (c->block_t == 256 && c->block_w == 224))) return FP8MM_E_CONFIG;
+    const bool small = c->block_w == 128 && (c->block_t == 16 || c->block_t == 32 || c->block_t == 64 || c->block_t == 128);
+    if (!((c->block_t == 128 && c->block_w == 256) || (c->block_t == 256 && c->block_w == 224) || small)) return FP8MM_E_CONFIG;
   } else if (c->impl == FP8MM_IMPL_GEMV) {
     if (c->block_w != kGemvRows) return FP8MM_E_CONFIG;
     if (c->block_t != 1 && c->block_t != 2 && c->block_t != 4) return FP8MM_E_CONFIG;
@@ -89,6 +90,34 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   }
   if (c->impl == FP8MM_IMPL_UMMA_MX) {
     g->mx = true;
+    if (c->block_w == 128) {
+      // swap-AB: 128 weight rows x block_t tokens, plain stores (no output tensor map), no split
+      g->swap = true;
+      g->tt = c->block_t;
+      g->wt = 128;
+      g->umma_n = g->tt;
+      g->t_tiles = (M + g->tt - 1) / g->tt;
+      g->w_tiles = N / 128;
+      g->tiles = g->t_tiles * g->w_tiles;
+      g->kb_total = g->kbn = K / 128;
+      g->split = 1;
+      g->kg = 1;
+      g->stg_slabs = 1;
+      g->threads = 6 * 32 + 4 * 32;
+      const size_t stage_bytes = 128 * 128 + (size_t)g->tt * 128;
+      const size_t fixed = 1024 + 2 * 1024 + sizeof(MxCtl);
+      int stages = c->stages > 0 ? c->stages : 8;
+      const int fit = (int)((kMaxDynSmem - fixed) / stage_bytes);
+      if (stages > fit) stages = fit;
+      if (stages > kMaxStages) stages = kMaxStages;
+      if (stages < 2) return FP8MM_E_CONFIG;
+      g->stages = stages;
+      size_t smem = fixed + (size_t)stages * stage_bytes;
+      const size_t tmem_cols = g->tt <= 16 ? 128 : (g->tt <= 32 ? 256 : 512);   // MxsTraits<TT>::TMEM_COLS
+      const size_t floor_smem = tmem_cols * 456 - 1024;     // shared-memory share >= TMEM share (see below)
+      g->smem = smem < floor_smem ? floor_smem : smem;
+      return FP8MM_OK;
+    }
     g->tt = c->block_t;
     g->wt = c->block_w;
     g->umma_n = g->wt;
@@ -336,7 +365,7 @@ int make_output_map(void* c, int m, int n, long long ldc, CUtensorMap* out, bool
 // ----------------------------------------------------------------- launch
 struct DeviceInfo {
   int sms = 0;
-  bool attr_set[42] = {};     // 0..35 tile kernels, 39 CTA-pair kernel, 40/41 block-scaled (UE8M0) kernels
+  bool attr_set[46] = {};     // 0..35 tile kernels, 39 CTA-pair kernel, 40/41 block-scaled (UE8M0) kernels
   // cluster split-K kernels: can a cluster of 2 / 4 / 8 such CTAs be placed at all?  0 = not asked
   // yet, 1 = yes, 2 = no (an SM-limited context, MPS or a green context can say no)
   unsigned char cluster_ok[40][4] = {};
@@ -731,6 +760,15 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
     if (cfg->max_ctas > 0 && pairs > cfg->max_ctas / 2) pairs = cfg->max_ctas / 2 > 0 ? cfg->max_ctas / 2 : 1;
     if (pairs > p.num_units) pairs = p.num_units;
     return launch_plain(fp8mm_umma_2cta_kernel, 39, dev, g, tm_tok, tm_wgt, outs, p, 2 * pairs, stream);
+  }
+  if (g.mx && g.swap) {
+    switch (g.tt) {
+      case 16: return launch_plain(fp8mm_mxs_kernel<16>, 42, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+      case 32: return launch_plain(fp8mm_mxs_kernel<32>, 43, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+      case 64: return launch_plain(fp8mm_mxs_kernel<64>, 44, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+      case 128: return launch_plain(fp8mm_mxs_kernel<128>, 45, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+    }
+    return FP8MM_E_CONFIG;
   }
   if (g.mx) {
     return g.tt == 256 ? launch_plain(fp8mm_mx256_kernel, 41, dev, g, tm_tok, tm_wgt, outs, p, grid, stream)

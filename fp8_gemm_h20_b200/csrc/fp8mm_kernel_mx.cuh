@@ -610,4 +610,255 @@ fp8mm_mx256_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_cons
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Small token counts with power-of-two scales: swap-AB tiles of 128 weight rows (on the 128 rows of
+// the MMA) x TT tokens (on its N), the whole K accumulated in tensor memory.  Nothing crosses registers
+// per K block (the table kernels promote every block), no split-K.  What paces such a CTA is the ISSUE
+// of the MMAs: ~90 cycles per tcgen05.mma for its thread, four per K block, whatever the tile's width.
+// So NI threads in NI warps issue, thread i the K blocks kb % NI == i, each into its OWN accumulator
+// (TT columns) and from its OWN copy of the scale words; the epilogue adds the NI accumulators in
+// issuer order.  Scale words: one atom for the weight rows (one scale block: every word the same), one
+// for the tokens.  Four epilogue warps read the accumulators 32 columns at a time and store bf16 with
+// plain stores (a thread owns a weight row = a column of C).
+// Warps: 0 producer, 1 scale loader, 2..5 MMA issuers (2..3 for 128 tokens), 6..9 epilogue.
+template <int TT>
+struct MxsTraits {
+  static_assert(TT == 16 || TT == 32 || TT == 64 || TT == 128, "token tile");
+  static constexpr int NI = TT <= 64 ? 4 : 2;                 // issuing threads = accumulators
+  static constexpr int SERVICE = 6 * 32;
+  static constexpr int THREADS = SERVICE + 4 * 32;
+  static constexpr uint32_t ROW_BYTES = 128u * 128u;          // 128 weight rows of one K block
+  static constexpr uint32_t COL_BYTES = (uint32_t)TT * 128u;  // TT tokens
+  static constexpr uint32_t STAGE_BYTES = ROW_BYTES + COL_BYTES;
+  static constexpr uint32_t SF_SLOT_BYTES = 2u * 512u;
+  static constexpr uint32_t SF_COL = (uint32_t)(NI * TT);     // per issuer and slot 8 columns
+  static constexpr uint32_t USED_COLS = SF_COL + NI * 16u;
+  static constexpr uint32_t TMEM_COLS = USED_COLS <= 32 ? 32u : (USED_COLS <= 64 ? 64u : (USED_COLS <= 128 ? 128u : (USED_COLS <= 256 ? 256u : 512u)));
+};
+
+template <int TT>
+__global__ void __launch_bounds__(MxsTraits<TT>::THREADS, 1)
+fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_constant__ CUtensorMap tm_wgt,
+                 const __grid_constant__ OutTargets outs, const KParams p) {
+  using T = MxsTraits<TT>;
+  constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES;
+  constexpr int NI = T::NI;
+
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  unsigned char* smem = smem_raw + pad;
+  const uint32_t ring = raw_addr + pad;
+
+  const int kbn = p.kb_per_unit;
+  const int stages = p.stages;
+  const uint32_t sf_smem = ring + stages * STAGE_BYTES;
+  MxCtl* ctl = reinterpret_cast<MxCtl*>(smem + (size_t)stages * STAGE_BYTES + 2 * T::SF_SLOT_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t bar_full = ptx::smem_u32(&ctl->full[0]);
+  const uint32_t bar_empty = ptx::smem_u32(&ctl->empty[0]);
+  const uint32_t bar_sffull = ptx::smem_u32(&ctl->sffull[0]);
+  const uint32_t bar_sfempty = ptx::smem_u32(&ctl->sfempty[0]);
+  const uint32_t bar_accfull = ptx::smem_u32(&ctl->accfull);
+  const uint32_t bar_accempty = ptx::smem_u32(&ctl->accempty);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(bar_full + 8 * s, 1);
+      // the commit of the thread that issued the block's MMAs, and a plain arrive of every other issuing
+      // thread once it has seen the slot full (each must see every fill of every slot, or its parity
+      // wait on a later fill could be answered by an earlier one)
+      ptx::mbar_init(bar_empty + 8 * s, NI);
+    }
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(bar_sffull + 8 * s, 32);
+      ptx::mbar_init(bar_sfempty + 8 * s, NI);
+    }
+    ptx::mbar_init(bar_accfull, NI);
+    ptx::mbar_init(bar_accempty, 4);
+    ctl->abort = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tm_tok);
+    ptx::prefetch_tensormap(&tm_wgt);
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc(ptx::smem_u32(&ctl->tmem_base), T::TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
+
+  BoundedWait bw{&ctl->abort, p.status, p.timeout_ns};
+  const unsigned char* As8 = reinterpret_cast<const unsigned char*>(p.As);
+  const unsigned char* Bs8 = reinterpret_cast<const unsigned char*>(p.Bs);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t ph = 0;
+      bool first_pass = true, ok = true;
+      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
+        const UnitCoord c = decode_unit(u, p);
+        for (int kb = 0; kb < kbn; ++kb) {
+          if (!first_pass && !bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
+          const uint32_t dst = ring + stage * STAGE_BYTES;
+          ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
+          ptx::tma_load_2d(dst, &tm_wgt, bar_full + 8 * stage, kb * 128, c.wi * 128);
+          ptx::tma_load_2d(dst + T::ROW_BYTES, &tm_tok, bar_full + 8 * stage, kb * 128, c.ti * TT);
+          if (++stage == stages) { stage = 0; ph ^= 1u; first_pass = false; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ scale loader
+    uint32_t gi = 0;
+    bool ok = true;
+    const int nblk_max = p.N / 128 - 1;
+    for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
+      const UnitCoord c = decode_unit(u, p);
+      for (int kb0 = 0; kb0 < kbn; kb0 += 4, ++gi) {
+        const uint32_t slot = gi & 1u, use = gi >> 1;
+        if (use > 0 && !bw.wait(bar_sfempty + 8 * slot, (use - 1) & 1u, kWaitMxLoaderEmpty)) { ok = false; break; }
+        uint32_t wt[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          wt[q] = 0x7F7F7F7Fu;
+          if (q * 32 < TT) {
+            const int tok = min(c.ti * TT + q * 32 + lane, p.M - 1);
+            const unsigned char* src = As8 + (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
+            uint32_t v = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              v |= ((kb0 + j < kbn) ? static_cast<uint32_t>(__ldg(src + (long long)j * p.as_sk)) : 127u) << (8 * j);
+            wt[q] = v;
+          }
+        }
+        const unsigned char* srcw = Bs8 + (long long)min(c.wi, nblk_max) * p.bs_sn + (long long)kb0 * p.bs_sk;
+        uint32_t ww = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          ww |= ((kb0 + j < kbn) ? static_cast<uint32_t>(__ldg(srcw + (long long)j * p.bs_sk)) : 127u) << (8 * j);
+        const uint32_t dst = sf_smem + slot * T::SF_SLOT_BYTES + lane * 16u;
+        ptx::sts_v4(dst, ww, ww, ww, ww);
+        ptx::sts_v4(dst + 512u, wt[0], wt[1], wt[2], wt[3]);
+        ptx::fence_proxy_async_smem();
+        ptx::mbar_arrive(bar_sffull + 8 * slot);
+      }
+    }
+  } else if (warp < 2 + NI) {
+    // ------------------------------------------------------------- MMA issuers
+    if (lane == 0) {
+      const uint32_t id = warp - 2;
+      const uint32_t d_tmem = tmem_base + id * TT;
+      int stage = 0;
+      uint32_t ph = 0, ui = 0, gi = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x, ++ui) {
+        if (ui > 0 && !bw.wait(bar_accempty, (ui - 1) & 1u, kWaitMxIssuerAcc)) break;
+        ptx::tc_fence_after();
+        bool first = true;         // this thread's first MMA of the unit overwrites its accumulator
+        for (int kb = 0; kb < kbn; ++kb) {
+          const uint32_t slot = gi & 1u;
+          const uint32_t tsf = tmem_base + T::SF_COL + id * 16u + slot * 8u;
+          if ((kb & 3) == 0) {
+            if (!bw.wait(bar_sffull + 8 * slot, (gi >> 1) & 1u, kWaitMxIssuerScales)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const uint32_t src = sf_smem + slot * T::SF_SLOT_BYTES;
+            ptx::tmem_cp_32x128b_warpx4(tsf, ptx::smem_desc_sf(src));
+            ptx::tmem_cp_32x128b_warpx4(tsf + 4u, ptx::smem_desc_sf(src + 512u));
+          }
+          if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
+          if ((uint32_t)kb % NI == id) {
+            ptx::tc_fence_after();
+            const uint32_t a_addr = ring + stage * STAGE_BYTES;
+            const uint64_t a_desc = ptx::smem_desc_k128(a_addr);
+            const uint64_t b_desc = ptx::smem_desc_k128(a_addr + T::ROW_BYTES);
+            const uint32_t idesc = ptx::idesc_mxf8_m128(TT, static_cast<uint32_t>(kb & 3));
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              ptx::umma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, tsf, tsf + 4u,
+                             static_cast<uint32_t>(!(first && k == 0)));
+            first = false;
+            ptx::umma_commit(bar_empty + 8 * stage);
+          } else {
+            ptx::mbar_arrive(bar_empty + 8 * stage);
+          }
+          if ((kb & 3) == 3 || kb == kbn - 1) {
+            ptx::umma_commit(bar_sfempty + 8 * slot);   // this thread's MMAs and copies of the group are done
+            ++gi;
+          }
+          if (++stage == stages) { stage = 0; ph ^= 1u; }
+        }
+        if (ok) ptx::umma_commit(bar_accfull);
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 6) {
+    // ---------------------------------------------------------- epilogue warps
+    const int q = warp & 3;
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    constexpr int CH = TT >= 32 ? 32 : 16;
+    const int n_acc = min(NI, kbn);          // issuers beyond the K blocks of a unit never wrote theirs
+    uint32_t ui = 0;
+    for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
+      const UnitCoord c = decode_unit(u, p);
+      if (!bw.wait(bar_accfull, ui & 1u, kWaitMxEpilogueAcc)) break;
+      ptx::tc_fence_after();
+      const int n = c.wi * 128 + q * 32 + lane;
+      const int m_base = c.ti * TT;
+#pragma unroll
+      for (int ch = 0; ch < TT / CH; ++ch) {
+        float acc[CH];
+        {
+          uint32_t d[CH];
+          ptx::tmem_ld<CH>(taddr + ch * CH, d);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < CH; ++j) acc[j] = __uint_as_float(d[j]);
+        }
+        for (int a = 1; a < n_acc; ++a) {
+          uint32_t d[CH];
+          ptx::tmem_ld<CH>(taddr + a * TT + ch * CH, d);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < CH; ++j) acc[j] += __uint_as_float(d[j]);
+        }
+        if (ch == TT / CH - 1) {
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bar_accempty);     // the accumulators may be overwritten
+        }
+        const int m_left = p.M - (m_base + ch * CH);
+        for (int t = 0; t < outs.n; ++t) {
+          __nv_bfloat16* dst = outs.ptr[t] + (long long)(m_base + ch * CH) * p.ldc + n;
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            if (j < m_left) *dst = __float2bfloat16_rn(acc[j]);
+            dst += p.ldc;
+          }
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    if (ctl->abort) __nanosleep(1000000);  // let copies that are still in flight land
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
 }  // namespace fp8mm

@@ -76,7 +76,19 @@ def ue8m0_bytes(scales):
     raise ValueError("UE8M0 scales come as uint8 exponents, int32 words of four exponents, or float32 powers of two")
 
 
-MX_MIN_TOKENS = 256       # below this the table-driven kernels on expanded scales are the faster path
+MX_MIN_TOKENS = 256       # from here on the token-major block-scaled kernels (128x256, 256x224 tiles)
+MXS_MIN_TOKENS = 48       # from here to MX_MIN_TOKENS the swap-AB block-scaled kernel, on wide enough layers;
+MXS_MIN_WIDTH = 2048      # below, the table-driven kernels on expanded scales are the faster path
+
+
+def _mxs_tile(m):
+    """Token tile of the swap-AB block-scaled kernel: a quarter of the tokens, as a power of two in
+    16..128 (timed on a B200 at 64 / 128 / 200 tokens: 16 / 32 / 64 fastest; the weight rows of a CTA
+    are then re-read by up to four token tiles out of L2)."""
+    t = 16
+    while t * 4 < m and t < 128:
+        t *= 2
+    return t
 
 
 def _mx_tile(m, n, k=2048, sms=148):
@@ -95,9 +107,10 @@ def matmul_ue8m0(A, B, As, Bs, *, profile="35b_tp1"):
     """`matmul` for power-of-two scales: A[M,K], B[N,K] float8_e4m3fn, As[M,K/128] and Bs[N/128,K/128]
     in any of the forms `ue8m0_bytes` takes -> bfloat16 C[M,N].
 
-    From MX_MIN_TOKENS tokens on the scales stay bytes and the tensor cores apply them
-    (`umma_mx`, tcgen05.mma kind::mxf8f6f4.block_scale: no shape table needed); below that the scales
-    are expanded to float32 and the call goes through `matmul` and the profile's table."""
+    From MX_MIN_TOKENS tokens on (and from MXS_MIN_TOKENS on layers at least MXS_MIN_WIDTH wide) the scales
+    stay bytes and the tensor cores apply them (`umma_mx`, tcgen05.mma kind::mxf8f6f4.block_scale: no shape
+    table needed); below that the scales are expanded to float32 and the call goes through `matmul` and the
+    profile's table."""
     import torch
     from . import engine
     from .dispatch import matmul
@@ -122,4 +135,7 @@ def matmul_ue8m0(A, B, As, Bs, *, profile="35b_tp1"):
         if m >= MX_MIN_TOKENS:
             bt, bw = _mx_tile(m, n, k)
             return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": bt, "BLOCK_W": bw})
+        if m >= MXS_MIN_TOKENS and n >= MXS_MIN_WIDTH:
+            return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": _mxs_tile(m), "BLOCK_W": 128, "NUM_STAGES": 8,
+                                                           "GROUP_SIZE_M": 1})
         return matmul(A, B, expand_ue8m0(a8)[:, :kb], expand_ue8m0(b8)[:, :kb], profile=profile)

@@ -52,7 +52,9 @@ extern "C" {
                                        BYTES (value 2^(b-127); strides in bytes), 128 x 256 tiles, FP32
                                        accumulation over the whole K in tensor memory, no split-K.  The
                                        native form of the reference adapter's DEEPGEMM_SCALE_UE8M0 mode
-                                       (sgl_patch/fp8mm_sglang_patch.py); block_t 128, block_w 256       */
+                                       (sgl_patch/fp8mm_sglang_patch.py).  (block_t, block_w) = (128, 256)
+                                       or (256, 224) token-major tiles, or (16|32|64|128, 128) swap-AB tiles
+                                       for up to a few hundred tokens                                    */
 
 /* cfg.flags: reduce split-K partials through the global workspace even where the cluster
  * (distributed shared memory) reduction is available (splits of 2, 4 and 8). */
