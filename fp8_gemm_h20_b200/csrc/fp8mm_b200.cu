@@ -101,12 +101,12 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
       g->tiles = g->t_tiles * g->w_tiles;
       g->kb_total = g->kbn = K / 128;
       g->split = 1;
-      g->kg = 1;
+      g->kg = g->tt <= 64 ? 4 : 2;           // K blocks per ring slot = issuing threads (MxsTraits<TT>::NI)
       g->stg_slabs = 1;
       g->threads = 6 * 32 + 4 * 32;
-      const size_t stage_bytes = 128 * 128 + (size_t)g->tt * 128;
+      const size_t stage_bytes = (size_t)g->kg * (128 * 128 + (size_t)g->tt * 128);
       const size_t fixed = 1024 + 2 * 1024 + sizeof(MxCtl);
-      int stages = c->stages > 0 ? c->stages : 8;
+      int stages = c->stages > 0 ? c->stages : 4;
       const int fit = (int)((kMaxDynSmem - fixed) / stage_bytes);
       if (stages > fit) stages = fit;
       if (stages > kMaxStages) stages = kMaxStages;

@@ -618,7 +618,9 @@ fp8mm_mx256_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_cons
 // of the MMAs: ~90 cycles per tcgen05.mma for its thread, four per K block, whatever the tile's width.
 // So NI threads in NI warps issue, thread i the K blocks kb % NI == i, each into its OWN accumulator
 // (TT columns) and from its OWN copy of the scale words; the epilogue adds the NI accumulators in
-// issuer order.  Scale words: one atom for the weight rows (one scale block: every word the same), one
+// issuer order.  A ring slot holds NI K blocks, fetched by ONE 3-D copy per operand (the producing
+// thread pays per copy too): thread i takes block i of every slot.  K blocks past the end of K arrive as
+// zeros (the copy's out-of-bounds fill) and add nothing.  Scale words: one atom for the weight rows (one scale block: every word the same), one
 // for the tokens.  Four epilogue warps read the accumulators 32 columns at a time and store bf16 with
 // plain stores (a thread owns a weight row = a column of C).
 // Warps: 0 producer, 1 scale loader, 2..5 MMA issuers (2..3 for 128 tokens), 6..9 epilogue.
@@ -630,7 +632,7 @@ struct MxsTraits {
   static constexpr int THREADS = SERVICE + 4 * 32;
   static constexpr uint32_t ROW_BYTES = 128u * 128u;          // 128 weight rows of one K block
   static constexpr uint32_t COL_BYTES = (uint32_t)TT * 128u;  // TT tokens
-  static constexpr uint32_t STAGE_BYTES = ROW_BYTES + COL_BYTES;
+  static constexpr uint32_t STAGE_BYTES = NI * (ROW_BYTES + COL_BYTES);   // NI K blocks per slot
   static constexpr uint32_t SF_SLOT_BYTES = 2u * 512u;
   static constexpr uint32_t SF_COL = (uint32_t)(NI * TT);     // per issuer and slot 8 columns
   static constexpr uint32_t USED_COLS = SF_COL + NI * 16u;
@@ -669,10 +671,7 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(bar_full + 8 * s, 1);
-      // the commit of the thread that issued the block's MMAs, and a plain arrive of every other issuing
-      // thread once it has seen the slot full (each must see every fill of every slot, or its parity
-      // wait on a later fill could be answered by an earlier one)
-      ptx::mbar_init(bar_empty + 8 * s, NI);
+      ptx::mbar_init(bar_empty + 8 * s, NI);       // every issuing thread's commit: each takes one block of the slot
     }
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(bar_sffull + 8 * s, 32);
@@ -709,12 +708,13 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
       bool first_pass = true, ok = true;
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
         const UnitCoord c = decode_unit(u, p);
-        for (int kb = 0; kb < kbn; ++kb) {
+        for (int kb = 0; kb < kbn; kb += NI) {
           if (!first_pass && !bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
           const uint32_t dst = ring + stage * STAGE_BYTES;
           ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
-          ptx::tma_load_2d(dst, &tm_wgt, bar_full + 8 * stage, kb * 128, c.wi * 128);
-          ptx::tma_load_2d(dst + T::ROW_BYTES, &tm_tok, bar_full + 8 * stage, kb * 128, c.ti * TT);
+          // slot layout: [weight tile kb] .. [weight tile kb+NI-1][token tile kb] .. [token tile kb+NI-1]
+          ptx::tma_load_3d(dst, &tm_wgt, bar_full + 8 * stage, 0, c.wi * 128, kb);
+          ptx::tma_load_3d(dst + NI * T::ROW_BYTES, &tm_tok, bar_full + 8 * stage, 0, c.ti * TT, kb);
           if (++stage == stages) { stage = 0; ph ^= 1u; first_pass = false; }
         }
       }
@@ -768,10 +768,11 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
         if (ui > 0 && !bw.wait(bar_accempty, (ui - 1) & 1u, kWaitMxIssuerAcc)) break;
         ptx::tc_fence_after();
         bool first = true;         // this thread's first MMA of the unit overwrites its accumulator
-        for (int kb = 0; kb < kbn; ++kb) {
+        for (int kb0 = 0; kb0 < kbn; kb0 += NI) {
+          const int kb = kb0 + (int)id;                       // this thread's block of the slot (zeros past K)
           const uint32_t slot = gi & 1u;
           const uint32_t tsf = tmem_base + T::SF_COL + id * 16u + slot * 8u;
-          if ((kb & 3) == 0) {
+          if ((kb0 & 3) == 0) {
             if (!bw.wait(bar_sffull + 8 * slot, (gi >> 1) & 1u, kWaitMxIssuerScales)) { ok = false; break; }
             ptx::tc_fence_after();
             const uint32_t src = sf_smem + slot * T::SF_SLOT_BYTES;
@@ -779,22 +780,18 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
             ptx::tmem_cp_32x128b_warpx4(tsf + 4u, ptx::smem_desc_sf(src + 512u));
           }
           if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
-          if ((uint32_t)kb % NI == id) {
-            ptx::tc_fence_after();
-            const uint32_t a_addr = ring + stage * STAGE_BYTES;
-            const uint64_t a_desc = ptx::smem_desc_k128(a_addr);
-            const uint64_t b_desc = ptx::smem_desc_k128(a_addr + T::ROW_BYTES);
-            const uint32_t idesc = ptx::idesc_mxf8_m128(TT, static_cast<uint32_t>(kb & 3));
+          ptx::tc_fence_after();
+          const uint32_t base = ring + stage * STAGE_BYTES;
+          const uint64_t a_desc = ptx::smem_desc_k128(base + id * T::ROW_BYTES);
+          const uint64_t b_desc = ptx::smem_desc_k128(base + NI * T::ROW_BYTES + id * T::COL_BYTES);
+          const uint32_t idesc = ptx::idesc_mxf8_m128(TT, static_cast<uint32_t>(kb & 3));
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              ptx::umma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, tsf, tsf + 4u,
-                             static_cast<uint32_t>(!(first && k == 0)));
-            first = false;
-            ptx::umma_commit(bar_empty + 8 * stage);
-          } else {
-            ptx::mbar_arrive(bar_empty + 8 * stage);
-          }
-          if ((kb & 3) == 3 || kb == kbn - 1) {
+          for (int k = 0; k < 4; ++k)
+            ptx::umma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, tsf, tsf + 4u,
+                           static_cast<uint32_t>(!(first && k == 0)));
+          first = false;
+          ptx::umma_commit(bar_empty + 8 * stage);
+          if (((kb0 + NI) & 3) == 0 || kb0 + NI >= kbn) {
             ptx::umma_commit(bar_sfempty + 8 * slot);   // this thread's MMAs and copies of the group are done
             ++gi;
           }
@@ -809,7 +806,7 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
     const int q = warp & 3;
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     constexpr int CH = TT >= 32 ? 32 : 16;
-    const int n_acc = min(NI, kbn);          // issuers beyond the K blocks of a unit never wrote theirs
+    constexpr int n_acc = NI;
     uint32_t ui = 0;
     for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
       const UnitCoord c = decode_unit(u, p);

@@ -77,14 +77,14 @@ def ue8m0_bytes(scales):
 
 
 MX_MIN_TOKENS = 256       # from here on the token-major block-scaled kernels (128x256, 256x224 tiles)
-MXS_MIN_TOKENS = 48       # from here to MX_MIN_TOKENS the swap-AB block-scaled kernel, on wide enough layers;
-MXS_MIN_WIDTH = 2048      # below, the table-driven kernels on expanded scales are the faster path
+MXS_MIN_TOKENS = 32       # from here to MX_MIN_TOKENS the swap-AB block-scaled kernel (from 64 where K < 1024),
+MXS_MIN_WIDTH = 2048      # on layers at least this wide; below, the table-driven kernels on expanded scales
 
 
 def _mxs_tile(m):
     """Token tile of the swap-AB block-scaled kernel: a quarter of the tokens, as a power of two in
-    16..128 (timed on a B200 at 64 / 128 / 200 tokens: 16 / 32 / 64 fastest; the weight rows of a CTA
-    are then re-read by up to four token tiles out of L2)."""
+    16..128 (timed on a B200 at 32...64 / 128 / 200 tokens: 16 / 32 / 64 fastest or within a few per cent
+    of it; the weight rows of a CTA are then re-read by up to four token tiles out of L2)."""
     t = 16
     while t * 4 < m and t < 128:
         t *= 2
@@ -135,7 +135,7 @@ def matmul_ue8m0(A, B, As, Bs, *, profile="35b_tp1"):
         if m >= MX_MIN_TOKENS:
             bt, bw = _mx_tile(m, n, k)
             return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": bt, "BLOCK_W": bw})
-        if m >= MXS_MIN_TOKENS and n >= MXS_MIN_WIDTH:
-            return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": _mxs_tile(m), "BLOCK_W": 128, "NUM_STAGES": 8,
+        if m >= (MXS_MIN_TOKENS if k >= 1024 else 2 * MXS_MIN_TOKENS) and n >= MXS_MIN_WIDTH:
+            return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": _mxs_tile(m), "BLOCK_W": 128, "NUM_STAGES": 4,
                                                            "GROUP_SIZE_M": 1})
         return matmul(A, B, expand_ue8m0(a8)[:, :kb], expand_ue8m0(b8)[:, :kb], profile=profile)
