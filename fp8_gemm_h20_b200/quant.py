@@ -77,18 +77,23 @@ def ue8m0_bytes(scales):
 
 
 MX_MIN_TOKENS = 256       # from here on the token-major block-scaled kernels (128x256, 256x224 tiles)
-MXS_MIN_TOKENS = 32       # from here to MX_MIN_TOKENS the swap-AB block-scaled kernel (from 64 where K < 1024),
-MXS_MIN_WIDTH = 2048      # on layers at least this wide; below, the table-driven kernels on expanded scales
+MXS_MIN_TOKENS = 32       # from here to MX_MIN_TOKENS the swap-AB block-scaled kernel; from 64 where K < 1024 or
+MXS_MIN_WIDTH = 2048      # the layer is narrower than this.  Below, the table-driven kernels on expanded scales.
 
 
-def _mxs_tile(m):
-    """Token tile of the swap-AB block-scaled kernel: a quarter of the tokens, as a power of two in
-    16..128 (timed on a B200 at 32...64 / 128 / 200 tokens: 16 / 32 / 64 fastest or within a few per cent
-    of it; the weight rows of a CTA are then re-read by up to four token tiles out of L2)."""
-    t = 16
-    while t * 4 < m and t < 128:
-        t *= 2
-    return t
+def _mxs_tile(m, n, k=2048, sms=148):
+    """Token tile (16..128) of the swap-AB block-scaled kernel by a cost model fitted to measurements on
+    a B200: waves of (weight tile, token tile) units over the SMs x K blocks x the time of a K block,
+    which is what its 16 KB of weights + T x 128 bytes of tokens cost on the ~65 B/clk path from L2, and
+    never less than ~300 cycles.  Small tiles spread a narrow layer over more SMs; large ones read the
+    weights fewer times."""
+    best = None
+    for t in (16, 32, 64, 128):
+        units = (n // 128) * -(-m // t)
+        cost = -(-units // sms) * max(300.0, (16384 + t * 128) / 65.0)
+        if best is None or cost < best[0] - 1e-9:
+            best = (cost, t)
+    return best[1]
 
 
 def _mx_tile(m, n, k=2048, sms=148):
@@ -107,7 +112,7 @@ def matmul_ue8m0(A, B, As, Bs, *, profile="35b_tp1"):
     """`matmul` for power-of-two scales: A[M,K], B[N,K] float8_e4m3fn, As[M,K/128] and Bs[N/128,K/128]
     in any of the forms `ue8m0_bytes` takes -> bfloat16 C[M,N].
 
-    From MX_MIN_TOKENS tokens on (and from MXS_MIN_TOKENS on layers at least MXS_MIN_WIDTH wide) the scales
+    From MXS_MIN_TOKENS tokens on (twice that on narrow layers or short K) the scales
     stay bytes and the tensor cores apply them (`umma_mx`, tcgen05.mma kind::mxf8f6f4.block_scale: no shape
     table needed); below that the scales are expanded to float32 and the call goes through `matmul` and the
     profile's table."""
@@ -135,7 +140,7 @@ def matmul_ue8m0(A, B, As, Bs, *, profile="35b_tp1"):
         if m >= MX_MIN_TOKENS:
             bt, bw = _mx_tile(m, n, k)
             return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": bt, "BLOCK_W": bw})
-        if m >= (MXS_MIN_TOKENS if k >= 1024 else 2 * MXS_MIN_TOKENS) and n >= MXS_MIN_WIDTH:
-            return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": _mxs_tile(m), "BLOCK_W": 128, "NUM_STAGES": 4,
-                                                           "GROUP_SIZE_M": 1})
+        if m >= (MXS_MIN_TOKENS if k >= 1024 and n >= MXS_MIN_WIDTH else 2 * MXS_MIN_TOKENS):
+            return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": _mxs_tile(m, n, k), "BLOCK_W": 128,
+                                                           "NUM_STAGES": 4, "GROUP_SIZE_M": 1})
         return matmul(A, B, expand_ue8m0(a8)[:, :kb], expand_ue8m0(b8)[:, :kb], profile=profile)
