@@ -54,7 +54,15 @@ bool cluster_split_allowed();
 int check_cfg(int M, int N, int K, const fp8mm_cfg* c) {
   if (c == nullptr) return FP8MM_E_NULL;
   if (M < 1 || N < 128 || K < 128 || (N % 128) != 0 || (K % 128) != 0) return FP8MM_E_SHAPE;
-  if ((c->flags & ~(FP8MM_FLAG_WORKSPACE_SPLIT | FP8MM_FLAG_K_PAIRS | FP8MM_FLAG_K_GROUP_MASK)) != 0) return FP8MM_E_CONFIG;
+  if ((c->flags & ~(FP8MM_FLAG_WORKSPACE_SPLIT | FP8MM_FLAG_K_PAIRS | FP8MM_FLAG_K_GROUP_MASK |
+                    FP8MM_FLAG_SCALES_UE8M0 | FP8MM_FLAG_ACT_SCALES_F32)) != 0)
+    return FP8MM_E_CONFIG;
+  if ((c->flags & FP8MM_FLAG_ACT_SCALES_F32) &&
+      !(c->impl == FP8MM_IMPL_UMMA_MX || (c->impl == FP8MM_IMPL_GEMV && (c->flags & FP8MM_FLAG_SCALES_UE8M0))))
+    return FP8MM_E_CONFIG;
+  // exponent-byte scales: the block-scaled kernels (always) and the decode kernel (on request)
+  if ((c->flags & FP8MM_FLAG_SCALES_UE8M0) && c->impl != FP8MM_IMPL_GEMV && c->impl != FP8MM_IMPL_UMMA_MX)
+    return FP8MM_E_CONFIG;
   if (c->split < 1 || c->group_m < 1 || c->stages < 0 || c->max_ctas < 0) return FP8MM_E_CONFIG;
   if (c->impl == FP8MM_IMPL_UMMA) {
     if (c->block_t != 128) return FP8MM_E_CONFIG;
@@ -554,6 +562,8 @@ int launch_gemv(int dev, const fp8mm_args* a, const fp8mm_cfg* cfg, void* const*
   p.B = static_cast<const unsigned char*>(a->B);
   p.As = a->As;
   p.Bs = a->Bs;
+  p.ue8m0 = (cfg->flags & FP8MM_FLAG_SCALES_UE8M0) ? 1 : 0;
+  p.act_f32 = (cfg->flags & FP8MM_FLAG_ACT_SCALES_F32) ? 1 : 0;
   p.n_out = 1 + n_extra;
   for (int d = 0; d < p.n_out; ++d) p.out[d] = static_cast<__nv_bfloat16*>(d == 0 ? a->C : extra_c[d - 1]);
   p.as_sm = a->as_stride_m;
@@ -740,6 +750,7 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
   p.stages = g.stages;
   p.stg_slabs = g.stg_slabs;
   p.kg = g.kg;
+  p.act_f32 = (cfg->flags & FP8MM_FLAG_ACT_SCALES_F32) ? 1 : 0;
   p.trace = nullptr;
 #ifdef FP8MM_TRACE
   if (const char* e = getenv("FP8MM_TRACE_PTR")) p.trace = reinterpret_cast<long long*>(strtoull(e, nullptr, 0));

@@ -47,7 +47,16 @@ struct GemvParams {
   int kw;           // warps per row group = min(n_kc, 8); a warp takes the chunks kw apart
   int groups;       // row groups per CTA pass; the CTA has kw * groups warps
   int n_rg;         // N / 8
+  int ue8m0;        // As and Bs point to UE8M0 exponent bytes (value 2^(b-127)), strides in bytes
+  int act_f32;      // ... but As holds floats after all (float32 powers of two from the quantiser)
 };
+
+// One scale: a float, or an exponent byte made into the float 2^(b-127) (b = 0 reads as 0).
+__device__ __forceinline__ float gemv_scale(const float* base, long long at, int ue8m0) {
+  if (ue8m0)
+    return __uint_as_float(static_cast<uint32_t>(__ldg(reinterpret_cast<const unsigned char*>(base) + at)) << 23);
+  return __ldg(base + at);
+}
 
 // Four e4m3 bytes -> two f16x2 registers (bytes 0,1 and bytes 2,3), exactly.
 __device__ __forceinline__ void e4m3x4_to_f16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
@@ -133,9 +142,9 @@ fp8mm_gemv_kernel(const GemvParams p) {
       for (int m = 0; m < MT; ++m) {
         const int tok = min(m0 + m, p.M - 1);
         araw[m] = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)tok * p.K + (size_t)kb * 128 + sub * 16));
-        as_reg[m] = __ldg(p.As + (long long)tok * p.as_sm + (long long)kb * p.as_sk);
+        as_reg[m] = gemv_scale(p.As, (long long)tok * p.as_sm + (long long)kb * p.as_sk, p.ue8m0 && !p.act_f32);
       }
-      bs = __ldg(p.Bs + (long long)((rg * R) >> 7) * p.bs_sn + (long long)kb * p.bs_sk);
+      bs = gemv_scale(p.Bs, (long long)((rg * R) >> 7) * p.bs_sn + (long long)kb * p.bs_sk, p.ue8m0);
     }
     uint32_t act[MT][8];
 #pragma unroll

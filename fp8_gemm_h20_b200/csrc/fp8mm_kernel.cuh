@@ -77,6 +77,7 @@ struct KParams {
   int stages;
   int stg_slabs;       // bf16 staging slabs (32 rows x 64 columns) per epilogue warp: 1 or 2
   int kg;              // K blocks per ring slot (1..8); > 1 only in the KG = 2 kernel variants
+  int act_f32;         // block-scaled kernels: As holds float32 powers of two (not exponent bytes)
   long long* trace;    // trace builds only (-DFP8MM_TRACE): clock stamps of CTA 0, else unused
 };
 

@@ -66,6 +66,13 @@ __host__ __device__ constexpr uint32_t idesc_mxf8_m128(uint32_t n, uint32_t sf) 
 
 }  // namespace ptx
 
+// UE8M0 byte of the activation scale at element `at`: read as a byte, or taken from the exponent field
+// of a float32 power of two (what a quantiser with power-of-two scales hands over as floats).
+__device__ __forceinline__ uint32_t mx_act_scale(const KParams& p, long long at) {
+  if (p.act_f32) return (__float_as_uint(__ldg(p.As + at)) >> 23) & 0xFFu;
+  return static_cast<uint32_t>(__ldg(reinterpret_cast<const unsigned char*>(p.As) + at));
+}
+
 struct __align__(8) MxCtl {
   unsigned long long full[kMaxStages];
   unsigned long long empty[kMaxStages];
@@ -236,11 +243,11 @@ fp8mm_mx_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_constan
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int tok = min(c.ti * 128 + q * 32 + lane, p.M - 1);
-          const unsigned char* src = As8 + (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
+          const long long at = (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
           uint32_t w = 0;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint32_t b = (kb0 + j < kbn) ? static_cast<uint32_t>(__ldg(src + (long long)j * p.as_sk)) : 127u;
+            const uint32_t b = (kb0 + j < kbn) ? mx_act_scale(p, at + (long long)j * p.as_sk) : 127u;
             w |= b << (8 * j);
           }
           wa[q] = w;
@@ -488,7 +495,7 @@ fp8mm_mx256_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_cons
     uint32_t gi = 0;
     bool ok = true;
     const int nblk_max = p.N / 128 - 1;
-    const bool quick_a = p.as_sk == 1 && (p.as_sm & 3) == 0 && (reinterpret_cast<unsigned long long>(As8) & 3ull) == 0;
+    const bool quick_a = !p.act_f32 && p.as_sk == 1 && (p.as_sm & 3) == 0 && (reinterpret_cast<unsigned long long>(As8) & 3ull) == 0;
     for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
       const UnitCoord c = decode_unit(u, p);
       for (int kb0 = 0; kb0 < kbn; kb0 += 4, ++gi) {
@@ -499,14 +506,14 @@ fp8mm_mx256_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_cons
 #pragma unroll
         for (int q = 0; q < 8; ++q) {        // token rows q * 32 + lane
           const int tok = min(c.ti * 256 + q * 32 + lane, p.M - 1);
-          const unsigned char* src = As8 + (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
+          const long long at = (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
           uint32_t v = 0;
           if (quick_a && whole) {
-            v = __ldg(reinterpret_cast<const uint32_t*>(src));
+            v = __ldg(reinterpret_cast<const uint32_t*>(As8 + at));
           } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              v |= ((kb0 + j < kbn) ? static_cast<uint32_t>(__ldg(src + (long long)j * p.as_sk)) : 127u) << (8 * j);
+              v |= ((kb0 + j < kbn) ? mx_act_scale(p, at + (long long)j * p.as_sk) : 127u) << (8 * j);
           }
           w[q] = v;
         }
@@ -736,11 +743,11 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
           wt[q] = 0x7F7F7F7Fu;
           if (q * 32 < TT) {
             const int tok = min(c.ti * TT + q * 32 + lane, p.M - 1);
-            const unsigned char* src = As8 + (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
+            const long long at = (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
             uint32_t v = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              v |= ((kb0 + j < kbn) ? static_cast<uint32_t>(__ldg(src + (long long)j * p.as_sk)) : 127u) << (8 * j);
+              v |= ((kb0 + j < kbn) ? mx_act_scale(p, at + (long long)j * p.as_sk) : 127u) << (8 * j);
             wt[q] = v;
           }
         }

@@ -47,7 +47,8 @@ def make_cfg(impl, config):
     return _lib.Cfg(impl=impl_id, block_t=int(c["BLOCK_T"]), block_w=int(c["BLOCK_W"]),
                     stages=int(c["NUM_STAGES"]), split=int(c["SPLIT"]),
                     group_m=int(c["GROUP_SIZE_M"]), max_ctas=int(c.get("MAX_CTAS", 0)),
-                    flags=(1 if c.get("SPLIT_VIA_WORKSPACE") else 0) | _k_group_flag(int(c.get("K_GROUP", 1))))
+                    flags=(1 if c.get("SPLIT_VIA_WORKSPACE") else 0) | _k_group_flag(int(c.get("K_GROUP", 1)))
+                    | (4 if c.get("SCALES_UE8M0") else 0) | (8 if c.get("ACT_SCALES_F32") else 0))
 
 
 def _workspace(torch, device, stream, nbytes):

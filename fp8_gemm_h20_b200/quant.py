@@ -76,9 +76,11 @@ def ue8m0_bytes(scales):
     raise ValueError("UE8M0 scales come as uint8 exponents, int32 words of four exponents, or float32 powers of two")
 
 
-MX_MIN_TOKENS = 256       # from here on the token-major block-scaled kernels (128x256, 256x224 tiles)
-MXS_MIN_TOKENS = 32       # from here to MX_MIN_TOKENS the swap-AB block-scaled kernel; from 64 where K < 1024 or
-MXS_MIN_WIDTH = 2048      # the layer is narrower than this.  Below, the table-driven kernels on expanded scales.
+MX_MIN_TOKENS = 256       # from here on the token-major block-scaled kernels (128x256, 256x224 tiles);
+GEMV_MAX_TOKENS = 4       # up to here the decode kernel, reading the exponent bytes itself; between the two the
+                          # swap-AB block-scaled kernel.  (Expanding the scales to float32 for the table
+                          # kernels costs two more launches per call, more than those kernels are ahead
+                          # anywhere in that range.)
 
 
 def _mxs_tile(m, n, k=2048, sms=148):
@@ -112,13 +114,12 @@ def matmul_ue8m0(A, B, As, Bs, *, profile="35b_tp1"):
     """`matmul` for power-of-two scales: A[M,K], B[N,K] float8_e4m3fn, As[M,K/128] and Bs[N/128,K/128]
     in any of the forms `ue8m0_bytes` takes -> bfloat16 C[M,N].
 
-    From MXS_MIN_TOKENS tokens on (twice that on narrow layers or short K) the scales
-    stay bytes and the tensor cores apply them (`umma_mx`, tcgen05.mma kind::mxf8f6f4.block_scale: no shape
-    table needed); below that the scales are expanded to float32 and the call goes through `matmul` and the
-    profile's table."""
+    The scales stay bytes all the way: up to GEMV_MAX_TOKENS tokens the decode kernel reads them, from
+    MX_MIN_TOKENS on the token-major and in between the swap-AB block-scaled kernels hand them to the
+    tensor cores (`umma_mx`, tcgen05.mma kind::mxf8f6f4.block_scale).  No shape table is involved, so any
+    N and K that are multiples of 128 work; `profile` is accepted for symmetry with `matmul`."""
     import torch
     from . import engine
-    from .dispatch import matmul
     if A.ndim != 2 or B.ndim != 2:
         raise ValueError("A and B must be rank-2 tensors")
     m, k = A.shape
@@ -134,13 +135,18 @@ def matmul_ue8m0(A, B, As, Bs, *, profile="35b_tp1"):
         raise ValueError("A and B must be contiguous row-major tensors")
     kb = k // 128
     with torch.cuda.device(A.device):
-        a8, b8 = ue8m0_bytes(As), ue8m0_bytes(Bs)
+        # float32 activation scales (what a quantiser with power-of-two scales returns as floats) go to the
+        # kernels as they are: they take the exponent field themselves, no conversion launch in front
+        act_f32 = As.dtype == torch.float32
+        a8, b8 = (As if act_f32 else ue8m0_bytes(As)), ue8m0_bytes(Bs)
         if a8.shape[0] != m or a8.shape[1] < kb or b8.shape[0] != n // 128 or b8.shape[1] < kb:
             raise ValueError("Expected As[M,K/128] and Bs[N/128,K/128] (packed words may pad K/128 up to a multiple of 4)")
+        extra = {"ACT_SCALES_F32": True} if act_f32 else {}
         if m >= MX_MIN_TOKENS:
             bt, bw = _mx_tile(m, n, k)
-            return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": bt, "BLOCK_W": bw})
-        if m >= (MXS_MIN_TOKENS if k >= 1024 and n >= MXS_MIN_WIDTH else 2 * MXS_MIN_TOKENS):
-            return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": _mxs_tile(m, n, k), "BLOCK_W": 128,
-                                                           "NUM_STAGES": 4, "GROUP_SIZE_M": 1})
-        return matmul(A, B, expand_ue8m0(a8)[:, :kb], expand_ue8m0(b8)[:, :kb], profile=profile)
+            return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": bt, "BLOCK_W": bw, **extra})
+        if m <= GEMV_MAX_TOKENS:
+            # one token per warp pass up to two tokens, else four
+            return engine.launch(A, B, a8, b8, "gemv", {"BLOCK_T": 1 if m <= 2 else 4, "SCALES_UE8M0": True, **extra})
+        return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": _mxs_tile(m, n, k), "BLOCK_W": 128,
+                                                       "NUM_STAGES": 4, "GROUP_SIZE_M": 1, **extra})

@@ -68,6 +68,13 @@ extern "C" {
  * memory, otherwise ignored.  The result bits do not depend on it. */
 #define FP8MM_FLAG_K_GROUP(n) (((n) & 15) << 8)
 #define FP8MM_FLAG_K_GROUP_MASK 0xF00
+/* cfg.flags, FP8MM_IMPL_GEMV: As and Bs point to UE8M0 exponent bytes (value 2^(b-127); strides in bytes)
+ * instead of floats, as they always do for FP8MM_IMPL_UMMA_MX (where the flag is accepted and redundant). */
+#define FP8MM_FLAG_SCALES_UE8M0 4
+/* cfg.flags, with exponent-byte scales (FP8MM_IMPL_UMMA_MX, or FP8MM_IMPL_GEMV with the flag above): As holds
+ * float32 powers of two after all (strides in elements), as a quantiser with power-of-two scales hands them
+ * over (SGLang's with scale_ue8m0=True); the kernels take the exponent field.  Bs stays bytes. */
+#define FP8MM_FLAG_ACT_SCALES_F32 8
 
 /*
  * Operands.  Strides are in ELEMENTS and are exactly the values the reference

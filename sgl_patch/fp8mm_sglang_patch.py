@@ -12,8 +12,8 @@ Environment:
   FP8MM_PROFILE=35b_tp1|122b_tp4   tuning profile (default 35b_tp1)
   FP8MM_HOME=/path/to/this/repo    prepended to sys.path
   FP8MM_DISABLE_DG_PRECOMPILE=1    also skip DeepGEMM's all-M JIT precompile, unused once patched
-  FP8MM_UE8M0_NATIVE=0             with FP8MM_UE8M0=1: always expand the power-of-two scales to float32 instead
-                                   of handing 256 tokens and more to the block-scaled tensor-core kernel
+  FP8MM_UE8M0_NATIVE=0             with FP8MM_UE8M0=1: expand packed power-of-two weight scales to float32 and use
+                                   the profile's table kernels instead of the kernels that take the exponents
   FP8MM_UE8M0=1                    also engage when SGLang runs with DEEPGEMM_SCALE_UE8M0 (its default
                                    on Blackwell): power-of-two scales are taken as float32, or expanded
                                    from the packed int32 form once per weight; the activation quantiser
@@ -96,9 +96,10 @@ if os.environ.get("FP8MM_ENABLE") == "1":
                                     scale_tma_aligned=False, scale_ue8m0=True)
                     if weight_scale.dtype != torch.float32:
                         from fp8_gemm_h20_b200 import quant
-                        if input.numel() // k >= quant.MX_MIN_TOKENS and os.environ.get("FP8MM_UE8M0_NATIVE", "1") != "0":
-                            # enough tokens for the tensor cores' own block scaling: the packed exponent
-                            # words go to the kernel as they are, the activation scales as exponent bytes
+                        if os.environ.get("FP8MM_UE8M0_NATIVE", "1") != "0":
+                            # the packed exponent words go to the kernels as they are and the float32
+                            # power-of-two activation scales too (the kernels take the exponent field): the
+                            # tensor cores' own block scaling from five tokens on, the decode kernel below
                             ws = weight_scale if weight_scale.shape[0] == n // 128 else weight_scale[::128]
                             out = quant.matmul_ue8m0(q, weight, s, ws, profile=profile)
                             if bias is not None:
