@@ -149,6 +149,9 @@ def main(argv=None):
     lib = Path(__file__).with_name("libfp8mm_b200_trace.so")
     if not lib.is_file():
         raise SystemExit(f"{lib} missing: python -m fp8_gemm_h20_b200.build --trace")
+    from .build import up_to_date
+    if not up_to_date(lib):
+        raise SystemExit(f"{lib} is older than the sources: python -m fp8_gemm_h20_b200.build --trace")
     os.environ["FP8MM_LIB"] = str(lib)
     import torch
     from . import engine, testing
