@@ -76,48 +76,75 @@ def ue8m0_bytes(scales):
     raise ValueError("UE8M0 scales come as uint8 exponents, int32 words of four exponents, or float32 powers of two")
 
 
-MX_MIN_TOKENS = 256       # from here on the token-major block-scaled kernels (128x256, 256x224 tiles);
-GEMV_MAX_TOKENS = 4       # up to here the decode kernel, reading the exponent bytes itself; between the two the
-                          # swap-AB block-scaled kernel.  (Expanding the scales to float32 for the table
-                          # kernels costs two more launches per call, more than those kernels are ahead
-                          # anywhere in that range.)
+GEMV_MAX_TOKENS = 2         # up to here always the decode kernel (it reads the exponent bytes itself);
+GEMV_MAX_TOKENS_SHORT = 8   # up to here on narrow layers with little work (_gemv_wins)
+
+# Cycles measured on a B200.  Swap-AB block-scaled tiles by token tile: one K block (bound by the issue of
+# tensor-core instructions up to 64 tokens, by the copies at 128).  Token-major tiles: one K block (bound by
+# shared-memory bandwidth), the accumulator drain per tile, and what a launch pays once (set-up, first
+# copies in flight, last drain).
+_MXS_PERIOD = {16: 300.0, 32: 315.0, 64: 380.0, 128: 750.0}
+_MX_TILES = {(128, 256): (790.0, 1500.0, 4000.0), (256, 224): (1200.0, 2600.0, 5000.0)}
+
+
+def _mxs_cost(m, n, k, t, sms=148):
+    units = (n // 128) * -(-m // t)
+    kb = max(1, k // 128)
+    drain = 24.0 * t + 300.0        # an epilogue of t two-byte stores per thread
+    period = _MXS_PERIOD[t] * (1.2 if t == 16 and m > 16 else 1.0)   # 16-token tiles sharing a weight tile: measured
+    return -(-units // sms) * (kb * period + drain)
+
+
+def _mx_cost(m, n, k, tile, sms=148):
+    period, drain, once = _MX_TILES[tile]
+    units = -(-m // tile[0]) * -(-n // tile[1])
+    return once + -(-units // sms) * (max(1, k // 128) * period + drain)
+
+
+def _gemv_wins(m, n, k):
+    """The decode kernel against the 16-token swap-AB tile: always for one or two tokens; up to 8 tokens where
+    the layer is at most 2048 rows (one wave of the decode kernel's CTAs) and the work, in passes of four
+    tokens, stays under what the tile kernel needs for its K blocks (timed: 4 x 2048 x 2048 4.0 us against
+    5.3, 8 x 1024 x 2048 3.8 against 5.0, but 8 x 2048 x 2048 6.9 against 5.0 and 4 x 3072 x 2048 7.3 against 5.3)."""
+    if m <= GEMV_MAX_TOKENS:
+        return True
+    return m <= GEMV_MAX_TOKENS_SHORT and n <= 2048 and 4 * -(-m // 4) * n * k <= 17e6
 
 
 def _mxs_tile(m, n, k=2048, sms=148):
-    """Token tile (16..128) of the swap-AB block-scaled kernel by a cost model fitted to measurements on
-    a B200: waves of (weight tile, token tile) units over the SMs x K blocks x the time of a K block,
-    which is what its 16 KB of weights + T x 128 bytes of tokens cost on the ~65 B/clk path from L2, and
-    never less than ~300 cycles.  Small tiles spread a narrow layer over more SMs; large ones read the
-    weights fewer times."""
-    best = None
-    for t in (16, 32, 64, 128):
-        units = (n // 128) * -(-m // t)
-        cost = -(-units // sms) * max(300.0, (16384 + t * 128) / 65.0)
-        if best is None or cost < best[0] - 1e-9:
-            best = (cost, t)
-    return best[1]
+    """Token tile (16..128) of the swap-AB block-scaled kernel: the cheapest by waves of (weight tile, token
+    tile) units over the SMs x K blocks x the time of a K block.  Small tiles spread a narrow layer over more
+    SMs; large ones read the weights fewer times."""
+    return min((16, 32, 64, 128), key=lambda t: (_mxs_cost(m, n, k, t, sms), t))
 
 
 def _mx_tile(m, n, k=2048, sms=148):
-    """128x256 or 256x224 tiles, by a cost model fitted to measurements on a B200: waves of tiles over
-    the SMs times the time of one tile = K blocks x block period + the accumulator drain
-    (128x256: ~790 cycles per K block + ~1500; 256x224: ~1200 + ~2600 for 1.75 x the work)."""
-    kb = max(1, k // 128)
+    """128x256 or 256x224 token-major tiles: the cheaper by waves of tiles x (K blocks x period + drain)."""
+    return min(_MX_TILES, key=lambda tile: (_mx_cost(m, n, k, tile, sms), tile))
 
-    def cost(t, w, period, drain):
-        units = -(-m // t) * -(-n // w)
-        return -(-units // sms) * (kb * period + drain)
-    return (256, 224) if cost(256, 224, 1200, 2600) < cost(128, 256, 790, 1500) else (128, 256)
+
+def plan_ue8m0(m, n, k, sms=148):
+    """(impl, config) of `matmul_ue8m0` for one problem: the decode kernel for one or two tokens (up to 8
+    where the layer is narrow or K short), else the cheaper of the swap-AB and the token-major block-scaled tiles by the cost
+    models above (the swap-AB tiles win wherever the token-major ones would leave most SMs without a tile:
+    up to ~1000 tokens on layers of a few thousand rows)."""
+    if _gemv_wins(m, n, k):
+        return "gemv", {"BLOCK_T": 1 if m <= 2 else 4, "SCALES_UE8M0": True}
+    t = _mxs_tile(m, n, k, sms)
+    tile = _mx_tile(m, n, k, sms)
+    if _mxs_cost(m, n, k, t, sms) <= _mx_cost(m, n, k, tile, sms):
+        return "umma_mx", {"BLOCK_T": t, "BLOCK_W": 128, "NUM_STAGES": 4, "GROUP_SIZE_M": 1}
+    return "umma_mx", {"BLOCK_T": tile[0], "BLOCK_W": tile[1]}
 
 
 def matmul_ue8m0(A, B, As, Bs, *, profile="35b_tp1"):
     """`matmul` for power-of-two scales: A[M,K], B[N,K] float8_e4m3fn, As[M,K/128] and Bs[N/128,K/128]
     in any of the forms `ue8m0_bytes` takes -> bfloat16 C[M,N].
 
-    The scales stay bytes all the way: up to GEMV_MAX_TOKENS tokens the decode kernel reads them, from
-    MX_MIN_TOKENS on the token-major and in between the swap-AB block-scaled kernels hand them to the
-    tensor cores (`umma_mx`, tcgen05.mma kind::mxf8f6f4.block_scale).  No shape table is involved, so any
-    N and K that are multiples of 128 work; `profile` is accepted for symmetry with `matmul`."""
+    The scales stay bytes all the way: the decode kernel reads them for one or two tokens, the swap-AB
+    and token-major block-scaled kernels hand them to the tensor cores (`umma_mx`, tcgen05.mma
+    kind::mxf8f6f4.block_scale); `plan_ue8m0` picks by measured cost models.  No shape table is involved, so
+    any N and K that are multiples of 128 work; `profile` is accepted for symmetry with `matmul`."""
     import torch
     from . import engine
     if A.ndim != 2 or B.ndim != 2:
@@ -141,12 +168,7 @@ def matmul_ue8m0(A, B, As, Bs, *, profile="35b_tp1"):
         a8, b8 = (As if act_f32 else ue8m0_bytes(As)), ue8m0_bytes(Bs)
         if a8.shape[0] != m or a8.shape[1] < kb or b8.shape[0] != n // 128 or b8.shape[1] < kb:
             raise ValueError("Expected As[M,K/128] and Bs[N/128,K/128] (packed words may pad K/128 up to a multiple of 4)")
-        extra = {"ACT_SCALES_F32": True} if act_f32 else {}
-        if m >= MX_MIN_TOKENS:
-            bt, bw = _mx_tile(m, n, k)
-            return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": bt, "BLOCK_W": bw, **extra})
-        if m <= GEMV_MAX_TOKENS:
-            # one token per warp pass up to two tokens, else four
-            return engine.launch(A, B, a8, b8, "gemv", {"BLOCK_T": 1 if m <= 2 else 4, "SCALES_UE8M0": True, **extra})
-        return engine.launch(A, B, a8, b8, "umma_mx", {"BLOCK_T": _mxs_tile(m, n, k), "BLOCK_W": 128,
-                                                       "NUM_STAGES": 4, "GROUP_SIZE_M": 1, **extra})
+        impl, conf = plan_ue8m0(m, n, k)
+        if act_f32:
+            conf = dict(conf, ACT_SCALES_F32=True)
+        return engine.launch(A, B, a8, b8, impl, conf)
