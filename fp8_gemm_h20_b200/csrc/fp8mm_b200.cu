@@ -44,7 +44,7 @@ struct Geometry {
   int stg_slabs;
   int kg;              // K blocks per ring slot (1..8)
   bool gemv;           // CUDA-core decode path: no tiles, no split, no scratch
-  bool mx;             // UE8M0 scales through the block-scaled MMA: 128 x 256 tiles, no split
+  bool mx;             // UE8M0 scales through the block-scaled MMA (split-K on the swap-AB tiles only)
   size_t counter_bytes, partial_bytes;
 };
 
@@ -99,7 +99,7 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
   if (c->impl == FP8MM_IMPL_UMMA_MX) {
     g->mx = true;
     if (c->block_w == 128) {
-      // swap-AB: 128 weight rows x block_t tokens, plain stores (no output tensor map), no split
+      // swap-AB: 128 weight rows x block_t tokens, plain stores (no output tensor map)
       g->swap = true;
       g->tt = c->block_t;
       g->wt = 128;
@@ -107,9 +107,13 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
       g->t_tiles = (M + g->tt - 1) / g->tt;
       g->w_tiles = N / 128;
       g->tiles = g->t_tiles * g->w_tiles;
-      g->kb_total = g->kbn = K / 128;
-      g->split = 1;
+      g->kb_total = K / 128;
       g->kg = g->tt <= 64 ? 4 : 2;           // K blocks per ring slot = issuing threads (MxsTraits<TT>::NI)
+      // split-K: a split that does not divide the K-block count runs unsplit, like the table kernels'
+      g->split = (c->split > 1 && g->kb_total % c->split == 0 && g->tiles <= kMaxSplitTiles) ? c->split : 1;
+      g->kbn = g->kb_total / g->split;
+      g->cluster = (g->split == 2 || g->split == 4 || g->split == 8) && cluster_split_allowed() &&
+                   !(c->flags & FP8MM_FLAG_WORKSPACE_SPLIT);
       g->stg_slabs = 1;
       g->threads = 6 * 32 + 4 * 32;
       const size_t stage_bytes = (size_t)g->kg * (128 * 128 + (size_t)g->tt * 128);
@@ -120,6 +124,11 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
       if (stages > kMaxStages) stages = kMaxStages;
       if (stages < 2) return FP8MM_E_CONFIG;
       g->stages = stages;
+      // the cluster reduction parks the fp32 partial tile in the (then idle) operand ring
+      if (g->cluster && (size_t)stages * stage_bytes < (size_t)g->tt * 128 * sizeof(float)) g->cluster = false;
+      const bool ws_split = g->split > 1 && !g->cluster;
+      g->counter_bytes = ws_split ? kCounterBytes : 0;
+      g->partial_bytes = ws_split ? (size_t)g->tiles * g->split * g->tt * 128 * sizeof(float) : 0;
       size_t smem = fixed + (size_t)stages * stage_bytes;
       const size_t tmem_cols = g->tt <= 16 ? 128 : (g->tt <= 32 ? 256 : 512);   // MxsTraits<TT>::TMEM_COLS
       const size_t floor_smem = tmem_cols * 456 - 1024;     // shared-memory share >= TMEM share (see below)
@@ -373,10 +382,10 @@ int make_output_map(void* c, int m, int n, long long ldc, CUtensorMap* out, bool
 // ----------------------------------------------------------------- launch
 struct DeviceInfo {
   int sms = 0;
-  bool attr_set[46] = {};     // 0..35 tile kernels, 39 CTA-pair kernel, 40/41 block-scaled (UE8M0) kernels
+  bool attr_set[54] = {};     // 0..35 tile kernels, 39 CTA-pair kernel, 40/41 block-scaled (UE8M0) kernels
   // cluster split-K kernels: can a cluster of 2 / 4 / 8 such CTAs be placed at all?  0 = not asked
   // yet, 1 = yes, 2 = no (an SM-limited context, MPS or a green context can say no)
-  unsigned char cluster_ok[40][4] = {};
+  unsigned char cluster_ok[54][4] = {};
 };
 DeviceInfo g_dev[kMaxDevices];
 
@@ -459,7 +468,8 @@ int launch_one(int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok, 
 // The kernels that exist in one form only: the CTA-pair kernel (slot 39) and the block-scaled one (40).
 typedef void (*PlainKernel)(const CUtensorMap, const CUtensorMap, const OutTargets, const KParams);
 int launch_plain(PlainKernel kern, int slot, int dev, const Geometry& g, const CUtensorMap& tm_tok,
-                 const CUtensorMap& tm_wgt, const OutTargets& outs, const KParams& p, int grid, cudaStream_t stream) {
+                 const CUtensorMap& tm_wgt, const OutTargets& outs, const KParams& p, int grid, cudaStream_t stream,
+                 int cluster = 0) {
   {
     std::lock_guard<std::mutex> lk(g_mu);
     if (!g_dev[dev].attr_set[slot]) {
@@ -481,8 +491,32 @@ int launch_plain(PlainKernel kern, int slot, int dev, const Geometry& g, const C
     attr[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
   }
+  if (cluster > 1) {                       // the split CTAs of a tile form one cluster
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = cluster;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   lc.attrs = attr;
   lc.numAttrs = na;
+  if (cluster > 1) {
+    const int si = cluster == 2 ? 0 : (cluster == 4 ? 1 : 2);
+    unsigned char known;
+    {
+      std::lock_guard<std::mutex> lk(g_mu);
+      known = g_dev[dev].cluster_ok[slot][si];
+    }
+    if (known == 0) {
+      int n = 0;
+      const cudaError_t q = cudaOccupancyMaxActiveClusters(&n, kern, &lc);
+      if (q != cudaSuccess) (void)cudaGetLastError();
+      known = (q == cudaSuccess && n > 0) ? 1 : 2;
+      std::lock_guard<std::mutex> lk(g_mu);
+      g_dev[dev].cluster_ok[slot][si] = known;
+    }
+    if (known == 2) return kClusterUnschedulable;
+  }
   const cudaError_t e = cudaLaunchKernelEx(&lc, kern, tm_tok, tm_wgt, outs, p);
   if (e != cudaSuccess) (void)cudaGetLastError();
   return e == cudaSuccess ? FP8MM_OK : FP8MM_E_LAUNCH;
@@ -773,13 +807,25 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
     return launch_plain(fp8mm_umma_2cta_kernel, 39, dev, g, tm_tok, tm_wgt, outs, p, 2 * pairs, stream);
   }
   if (g.mx && g.swap) {
+    // slots 42..45 unsplit, 46..49 split-K through the workspace, 50..53 through a cluster
+    PlainKernel kern[3] = {nullptr, nullptr, nullptr};
+    int slot = 0;
     switch (g.tt) {
-      case 16: return launch_plain(fp8mm_mxs_kernel<16>, 42, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
-      case 32: return launch_plain(fp8mm_mxs_kernel<32>, 43, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
-      case 64: return launch_plain(fp8mm_mxs_kernel<64>, 44, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
-      case 128: return launch_plain(fp8mm_mxs_kernel<128>, 45, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+      case 16: kern[0] = fp8mm_mxs_kernel<16, 0>; kern[1] = fp8mm_mxs_kernel<16, 1>; kern[2] = fp8mm_mxs_kernel<16, 2>; slot = 42; break;
+      case 32: kern[0] = fp8mm_mxs_kernel<32, 0>; kern[1] = fp8mm_mxs_kernel<32, 1>; kern[2] = fp8mm_mxs_kernel<32, 2>; slot = 43; break;
+      case 64: kern[0] = fp8mm_mxs_kernel<64, 0>; kern[1] = fp8mm_mxs_kernel<64, 1>; kern[2] = fp8mm_mxs_kernel<64, 2>; slot = 44; break;
+      case 128: kern[0] = fp8mm_mxs_kernel<128, 0>; kern[1] = fp8mm_mxs_kernel<128, 1>; kern[2] = fp8mm_mxs_kernel<128, 2>; slot = 45; break;
+      default: return FP8MM_E_CONFIG;
     }
-    return FP8MM_E_CONFIG;
+    if (g.split == 1) return launch_plain(kern[0], slot, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
+    if (g.cluster) {
+      // one CTA per unit, the `split` CTAs of a tile in one cluster; without room for such a cluster in this
+      // context the workspace reduction gives the same bits, if the caller's workspace is large enough
+      const int rc = launch_plain(kern[2], slot + 8, dev, g, tm_tok, tm_wgt, outs, p, p.num_units, stream, g.split);
+      if (rc != kClusterUnschedulable) return rc;
+      if (p.ws_partial == nullptr) return FP8MM_E_WORKSPACE;
+    }
+    return launch_plain(kern[1], slot + 4, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
   }
   if (g.mx) {
     return g.tt == 256 ? launch_plain(fp8mm_mx256_kernel, 41, dev, g, tm_tok, tm_wgt, outs, p, grid, stream)

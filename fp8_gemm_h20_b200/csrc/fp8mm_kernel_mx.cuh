@@ -82,6 +82,8 @@ struct __align__(8) MxCtl {
   unsigned long long accempty;
   unsigned int tmem_base;
   int abort;
+  int last;      // split-K: verdict of the tile's counter for this CTA's epilogue warps
+  int reserved;
 };
 
 // Codes of the waits of this kernel (role * 16 + barrier kind), next to those of fp8mm_umma_kernel.
@@ -621,15 +623,18 @@ fp8mm_mx256_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_cons
 // ---------------------------------------------------------------------------------------------
 // Small token counts with power-of-two scales: swap-AB tiles of 128 weight rows (on the 128 rows of
 // the MMA) x TT tokens (on its N), the whole K accumulated in tensor memory.  Nothing crosses registers
-// per K block (the table kernels promote every block), no split-K.  What paces such a CTA is the ISSUE
+// per K block (the table kernels promote every block).  What paces such a CTA is the ISSUE
 // of the MMAs: ~90 cycles per tcgen05.mma for its thread, four per K block, whatever the tile's width.
 // So NI threads in NI warps issue, thread i the K blocks kb % NI == i, each into its OWN accumulator
 // (TT columns) and from its OWN copy of the scale words; the epilogue adds the NI accumulators in
 // issuer order.  A ring slot holds NI K blocks, fetched by ONE 3-D copy per operand (the producing
-// thread pays per copy too): thread i takes block i of every slot.  K blocks past the end of K arrive as
-// zeros (the copy's out-of-bounds fill) and add nothing.  Scale words: one atom for the weight rows (one scale block: every word the same), one
+// thread pays per copy too): thread i takes block i of every slot; blocks of the last slot past the unit's K range are not used.  Scale words: one atom for the weight rows (one scale block: every word the same), one
 // for the tokens.  Four epilogue warps read the accumulators 32 columns at a time and store bf16 with
 // plain stores (a thread owns a weight row = a column of C).
+// Split-K (layers with too few weight tiles for the SMs): units of (tile, K split).  With a split of 2, 4 or
+// 8 the CTAs of a tile form a cluster, park their fp32 partials in their own shared memory and rank r adds
+// the r-th slice of token columns over distributed shared memory; otherwise every unit parks its partial in
+// the workspace and the last one to arrive on the tile's counter adds them.  Both add in split order.
 // Warps: 0 producer, 1 scale loader, 2..5 MMA issuers (2..3 for 128 tokens), 6..9 epilogue.
 template <int TT>
 struct MxsTraits {
@@ -646,13 +651,58 @@ struct MxsTraits {
   static constexpr uint32_t TMEM_COLS = USED_COLS <= 32 ? 32u : (USED_COLS <= 64 ? 64u : (USED_COLS <= 128 ? 128u : (USED_COLS <= 256 ? 256u : 512u)));
 };
 
+// Split-K tail of fp8mm_mxs_kernel: add the fp32 partials of one tile in split order and write bf16.  Called by
+// the four epilogue warps of the CTA that arrived last on the tile's counter; kept out of line so that the
+// common path's registers do not pay for it.
 template <int TT>
+__device__ __noinline__ void mxs_reduce_tile(const float* base, int split, int M, long long ldc,
+                                             const OutTargets& outs, int m_base, int n) {
+  const size_t tile_floats = (size_t)TT * 128;
+  constexpr int RC = 16;             // token columns per pass
+  constexpr int SG = 4;              // splits whose loads are in flight together (one L2 round trip)
+#pragma unroll 1
+  for (int c0 = 0; c0 < TT; c0 += RC) {
+    if (m_base + c0 >= M) break;
+    float acc[RC];
+    for (int s0 = 0; s0 < split; s0 += SG) {
+      float v[SG][RC];
+#pragma unroll
+      for (int ss = 0; ss < SG; ++ss) {
+        if (s0 + ss < split) {
+          const float* src = base + (size_t)(s0 + ss) * tile_floats + (size_t)c0 * 128;
+#pragma unroll
+          for (int j = 0; j < RC; ++j) v[ss][j] = __ldcg(src + (size_t)j * 128);
+        }
+      }
+#pragma unroll
+      for (int ss = 0; ss < SG; ++ss) {
+        if (s0 + ss < split) {
+#pragma unroll
+          for (int j = 0; j < RC; ++j) acc[j] = (s0 + ss == 0) ? v[ss][j] : acc[j] + v[ss][j];
+        }
+      }
+    }
+    const int m_left = M - (m_base + c0);
+    for (int t = 0; t < outs.n; ++t) {
+      __nv_bfloat16* dst = outs.ptr[t] + (long long)(m_base + c0) * ldc + n;
+#pragma unroll
+      for (int j = 0; j < RC; ++j) {
+        if (j < m_left) *dst = __float2bfloat16_rn(acc[j]);
+        dst += ldc;
+      }
+    }
+  }
+}
+
+// SPLITK: 0 = one unit per tile, 1 = split-K through the workspace, 2 = through a cluster.
+template <int TT, int SPLITK = 0>
 __global__ void __launch_bounds__(MxsTraits<TT>::THREADS, 1)
 fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_constant__ CUtensorMap tm_wgt,
                  const __grid_constant__ OutTargets outs, const KParams p) {
   using T = MxsTraits<TT>;
   constexpr uint32_t STAGE_BYTES = T::STAGE_BYTES;
   constexpr int NI = T::NI;
+  constexpr bool kSplit = SPLITK != 0;
 
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -715,13 +765,14 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
       bool first_pass = true, ok = true;
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
         const UnitCoord c = decode_unit(u, p);
+        const int kbo = kSplit ? c.s * kbn : 0;    // this split's first K block
         for (int kb = 0; kb < kbn; kb += NI) {
           if (!first_pass && !bw.wait(bar_empty + 8 * stage, ph ^ 1u, kWaitProducerEmpty)) { ok = false; break; }
           const uint32_t dst = ring + stage * STAGE_BYTES;
           ptx::mbar_arrive_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
           // slot layout: [weight tile kb] .. [weight tile kb+NI-1][token tile kb] .. [token tile kb+NI-1]
-          ptx::tma_load_3d(dst, &tm_wgt, bar_full + 8 * stage, 0, c.wi * 128, kb);
-          ptx::tma_load_3d(dst + NI * T::ROW_BYTES, &tm_tok, bar_full + 8 * stage, 0, c.ti * TT, kb);
+          ptx::tma_load_3d(dst, &tm_wgt, bar_full + 8 * stage, 0, c.wi * 128, kbo + kb);
+          ptx::tma_load_3d(dst + NI * T::ROW_BYTES, &tm_tok, bar_full + 8 * stage, 0, c.ti * TT, kbo + kb);
           if (++stage == stages) { stage = 0; ph ^= 1u; first_pass = false; }
         }
       }
@@ -734,6 +785,7 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
     const int nblk_max = p.N / 128 - 1;
     for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
       const UnitCoord c = decode_unit(u, p);
+      const int kbo = kSplit ? c.s * kbn : 0;
       for (int kb0 = 0; kb0 < kbn; kb0 += 4, ++gi) {
         const uint32_t slot = gi & 1u, use = gi >> 1;
         if (use > 0 && !bw.wait(bar_sfempty + 8 * slot, (use - 1) & 1u, kWaitMxLoaderEmpty)) { ok = false; break; }
@@ -743,7 +795,7 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
           wt[q] = 0x7F7F7F7Fu;
           if (q * 32 < TT) {
             const int tok = min(c.ti * TT + q * 32 + lane, p.M - 1);
-            const long long at = (long long)tok * p.as_sm + (long long)kb0 * p.as_sk;
+            const long long at = (long long)tok * p.as_sm + (long long)(kbo + kb0) * p.as_sk;
             uint32_t v = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j)
@@ -751,7 +803,7 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
             wt[q] = v;
           }
         }
-        const unsigned char* srcw = Bs8 + (long long)min(c.wi, nblk_max) * p.bs_sn + (long long)kb0 * p.bs_sk;
+        const unsigned char* srcw = Bs8 + (long long)min(c.wi, nblk_max) * p.bs_sn + (long long)(kbo + kb0) * p.bs_sk;
         uint32_t ww = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j)
@@ -776,7 +828,7 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
         ptx::tc_fence_after();
         bool first = true;         // this thread's first MMA of the unit overwrites its accumulator
         for (int kb0 = 0; kb0 < kbn; kb0 += NI) {
-          const int kb = kb0 + (int)id;                       // this thread's block of the slot (zeros past K)
+          const int kb = kb0 + (int)id;                       // this thread's block of the slot
           const uint32_t slot = gi & 1u;
           const uint32_t tsf = tmem_base + T::SF_COL + id * 16u + slot * 8u;
           if ((kb0 & 3) == 0) {
@@ -788,15 +840,19 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
           }
           if (!bw.wait(bar_full + 8 * stage, ph, kWaitMmaFull)) { ok = false; break; }
           ptx::tc_fence_after();
-          const uint32_t base = ring + stage * STAGE_BYTES;
-          const uint64_t a_desc = ptx::smem_desc_k128(base + id * T::ROW_BYTES);
-          const uint64_t b_desc = ptx::smem_desc_k128(base + NI * T::ROW_BYTES + id * T::COL_BYTES);
-          const uint32_t idesc = ptx::idesc_mxf8_m128(TT, static_cast<uint32_t>(kb & 3));
+          // the last slot of a split's K range reaches into the next split's blocks: not used.  (Unsplit, the
+          // blocks past K arrive as zeros, the copy's out-of-bounds fill, and add nothing.)
+          if (!kSplit || kb < kbn) {
+            const uint32_t base = ring + stage * STAGE_BYTES;
+            const uint64_t a_desc = ptx::smem_desc_k128(base + id * T::ROW_BYTES);
+            const uint64_t b_desc = ptx::smem_desc_k128(base + NI * T::ROW_BYTES + id * T::COL_BYTES);
+            const uint32_t idesc = ptx::idesc_mxf8_m128(TT, static_cast<uint32_t>(kb & 3));
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            ptx::umma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, tsf, tsf + 4u,
-                           static_cast<uint32_t>(!(first && k == 0)));
-          first = false;
+            for (int k = 0; k < 4; ++k)
+              ptx::umma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, tsf, tsf + 4u,
+                             static_cast<uint32_t>(!(first && k == 0)));
+            first = false;
+          }
           ptx::umma_commit(bar_empty + 8 * stage);
           if (((kb0 + NI) & 3) == 0 || kb0 + NI >= kbn) {
             ptx::umma_commit(bar_sfempty + 8 * slot);   // this thread's MMAs and copies of the group are done
@@ -813,16 +869,25 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
     const int q = warp & 3;
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     constexpr int CH = TT >= 32 ? 32 : 16;
-    constexpr int n_acc = NI;
+    const int n_acc = (kSplit && kbn < NI) ? kbn : NI;     // issuing threads that had a K block in this unit
+    const bool leader = threadIdx.x == T::SERVICE;
+    const size_t tile_floats = (size_t)TT * 128;
     uint32_t ui = 0;
     for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++ui) {
       const UnitCoord c = decode_unit(u, p);
-      if (!bw.wait(bar_accfull, ui & 1u, kWaitMxEpilogueAcc)) break;
-      ptx::tc_fence_after();
-      const int n = c.wi * 128 + q * 32 + lane;
+      const int row = q * 32 + lane;
+      const int n = c.wi * 128 + row;
       const int m_base = c.ti * TT;
+      // split-K: this unit's fp32 partial goes to the workspace, [token column][128 weight rows]
+      float* part = SPLITK == 1 ? p.ws_partial + ((size_t)c.tile * p.split + c.s) * tile_floats + row : nullptr;
+      const bool ok = bw.wait(bar_accfull, ui & 1u, kWaitMxEpilogueAcc);
+      if (!ok && part == nullptr) break;
+      // (with split-K a warp whose wait gave up still meets the other three at the barrier below, where
+      // the leader sees the abort flag and all four leave together)
+      ptx::tc_fence_after();
 #pragma unroll
       for (int ch = 0; ch < TT / CH; ++ch) {
+        if (!ok) break;
         float acc[CH];
         {
           uint32_t d[CH];
@@ -843,6 +908,19 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar_accempty);     // the accumulators may be overwritten
         }
+        if constexpr (SPLITK == 2) {
+          // cluster split-K: the partial waits in this CTA's own shared memory (the operand ring is idle: the
+          // CTA's only unit is finished), [token column][128 weight rows]; the reduction follows below
+          float* red = reinterpret_cast<float*>(smem) + row;
+#pragma unroll
+          for (int j = 0; j < CH; ++j) red[(ch * CH + j) * 128] = acc[j];
+          continue;
+        }
+        if constexpr (SPLITK == 1) {
+#pragma unroll
+          for (int j = 0; j < CH; ++j) __stcg(part + (size_t)(ch * CH + j) * 128, acc[j]);
+          continue;
+        }
         const int m_left = p.M - (m_base + ch * CH);
         for (int t = 0; t < outs.n; ++t) {
           __nv_bfloat16* dst = outs.ptr[t] + (long long)(m_base + ch * CH) * p.ldc + n;
@@ -853,7 +931,78 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
           }
         }
       }
+      if constexpr (SPLITK == 2) break;
+      if constexpr (SPLITK == 1) {
+        // The CTA that arrives last on the tile's counter adds all partials in split order (the same bits
+        // whichever CTA that is) and writes the tile; the counter goes back to zero for the next call.
+        __threadfence();
+        ptx::bar_sync(1, 128);
+        if (leader) {
+          int verdict = 2;  // 2 = a wait gave up somewhere in this CTA: stop
+          if (!ctl->abort) {
+            const int old = atomicAdd(p.ws_counter + c.tile, 1);
+            verdict = (old == p.split - 1) ? 1 : 0;
+          }
+          ctl->last = verdict;
+        }
+        ptx::bar_sync(1, 128);
+        const int verdict = ctl->last;
+        if (verdict == 2) break;
+        if (verdict == 0) continue;
+        __threadfence();
+        mxs_reduce_tile<TT>(p.ws_partial + (size_t)c.tile * p.split * tile_floats + row, p.split, p.M, p.ldc, outs,
+                            m_base, n);
+        if (leader) atomicExch(p.ws_counter + c.tile, 0);
+      }
     }
+  }
+
+  if constexpr (SPLITK == 2) {
+    // ------------------------------------------------- cluster split-K reduction
+    // Rank r adds the token columns [r, r+1) * TT / split of all ranks' partials in rank order (the order of
+    // the workspace path: the same bits) and writes them.  A rank whose bounded wait gave up has parked
+    // nothing: then no rank stores the tile.
+    ptx::cluster_sync_all();             // every CTA's partial is in its shared memory
+    if (warp >= 6 && blockIdx.x < p.num_units) {
+      const UnitCoord c = decode_unit(blockIdx.x, p);
+      const int row = (warp & 3) * 32 + lane;
+      uint32_t bad = 0;
+      {
+        const uint32_t abort_addr = ptx::smem_u32(&ctl->abort);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          if (s < p.split) bad |= ptx::ld_cluster_u32(ptx::map_to_cta(abort_addr, s));
+      }
+      const int cpr = TT / p.split;
+      const int col0 = (int)ptx::cluster_ctarank() * cpr;
+      const uint32_t rbase = ring + (uint32_t)row * 4u;
+      const int n = c.wi * 128 + row;
+      for (int j0 = 0; j0 < cpr; j0 += 4) {
+        float x[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
+            x[u][s] = 0.f;
+            if (s < p.split && j0 + u < cpr)
+              x[u][s] = ptx::ld_cluster_f32(ptx::map_to_cta(rbase + (uint32_t)(col0 + j0 + u) * 512u, s));
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float v = x[u][0];
+#pragma unroll
+          for (int s = 1; s < 8; ++s)
+            if (s < p.split) v += x[u][s];
+          const int m = c.ti * TT + col0 + j0 + u;
+          if (j0 + u < cpr && m < p.M && bad == 0) {
+            const __nv_bfloat16 b = __float2bfloat16_rn(v);
+            for (int t = 0; t < outs.n; ++t) outs.ptr[t][(long long)m * p.ldc + n] = b;
+          }
+        }
+      }
+    }
+    ptx::cluster_sync_all();             // no rank reads this CTA's shared memory any more
   }
 
   ptx::tc_fence_before();

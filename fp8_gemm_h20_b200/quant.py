@@ -118,6 +118,21 @@ def _mxs_tile(m, n, k=2048, sms=148):
     return min((16, 32, 64, 128), key=lambda t: (_mxs_cost(m, n, k, t, sms), t))
 
 
+def _mxs_split(m, n, k, t):
+    """Split-K of the swap-AB block-scaled kernel: 8 or 4 CTAs per tile (one cluster, partials added over
+    distributed shared memory) where K is long (24 blocks or more) and the tiles alone would leave most of
+    the GPU idle (tiles x split <= 64).  Measured: 4 x 512 x 3072 4.6 us against 6.0 unsplit, 8 x 2048 x 4096
+    5.9 against 7.4; with 16 K blocks, or more CTAs than that, the clusters' fixed cost (~1 us) eats the gain."""
+    kb = k // 128
+    units = (n // 128) * -(-m // t)
+    if kb < 24:
+        return 1
+    for s in (8, 4):
+        if kb % s == 0 and units * s <= 64:
+            return s
+    return 1
+
+
 def _mx_tile(m, n, k=2048, sms=148):
     """128x256 or 256x224 token-major tiles: the cheaper by waves of tiles x (K blocks x period + drain)."""
     return min(_MX_TILES, key=lambda tile: (_mx_cost(m, n, k, tile, sms), tile))
@@ -133,7 +148,8 @@ def plan_ue8m0(m, n, k, sms=148):
     t = _mxs_tile(m, n, k, sms)
     tile = _mx_tile(m, n, k, sms)
     if _mxs_cost(m, n, k, t, sms) <= _mx_cost(m, n, k, tile, sms):
-        return "umma_mx", {"BLOCK_T": t, "BLOCK_W": 128, "NUM_STAGES": 4, "GROUP_SIZE_M": 1}
+        return "umma_mx", {"BLOCK_T": t, "BLOCK_W": 128, "NUM_STAGES": 4, "GROUP_SIZE_M": 1,
+                           "SPLIT": _mxs_split(m, n, k, t)}
     return "umma_mx", {"BLOCK_T": tile[0], "BLOCK_W": tile[1]}
 
 

@@ -49,12 +49,14 @@ extern "C" {
                                        with the M<=8 entries of configs/122b_tp4.json)               */
 #define FP8MM_IMPL_UMMA_MX     4    /* power-of-two scales applied by the tensor cores themselves
                                        (tcgen05.mma kind::mxf8f6f4.block_scale): As and Bs point to UE8M0
-                                       BYTES (value 2^(b-127); strides in bytes), 128 x 256 tiles, FP32
-                                       accumulation over the whole K in tensor memory, no split-K.  The
-                                       native form of the reference adapter's DEEPGEMM_SCALE_UE8M0 mode
-                                       (sgl_patch/fp8mm_sglang_patch.py).  (block_t, block_w) = (128, 256)
-                                       or (256, 224) token-major tiles, or (16|32|64|128, 128) swap-AB tiles
-                                       for up to a few hundred tokens                                    */
+                                       BYTES (value 2^(b-127); strides in bytes), FP32 accumulation over
+                                       the K range in tensor memory.  The native form of the reference
+                                       adapter's DEEPGEMM_SCALE_UE8M0 mode (sgl_patch/fp8mm_sglang_patch.py).
+                                       (block_t, block_w) = (128, 256) or (256, 224) token-major tiles (no
+                                       split-K), or (16|32|64|128, 128) swap-AB tiles for up to a few hundred
+                                       tokens; these take cfg.split like the table kernels (cluster
+                                       reduction for 2, 4, 8, the workspace otherwise; a split that does not
+                                       divide K/128 runs unsplit)                                        */
 
 /* cfg.flags: reduce split-K partials through the global workspace even where the cluster
  * (distributed shared memory) reduction is available (splits of 2, 4 and 8). */
