@@ -694,6 +694,56 @@ __device__ __noinline__ void mxs_reduce_tile(const float* base, int split, int M
   }
 }
 
+// Cluster split-K tail of fp8mm_mxs_kernel: the partials lie [token column][128 weight rows]; this rank owns
+// the token columns [rank, rank + 1) * TT / S, warp pw of the four epilogue warps every fourth of them, a lane
+// four consecutive weight rows: 16-byte loads from the S ranks' shared memory, up to 16 in flight per lane (a
+// load from another SM takes about a microsecond), added in rank order, 8-byte stores (256 contiguous bytes per warp).
+template <int TT, int S>
+__device__ __forceinline__ void mxs_reduce_cols(uint32_t ring, int pw, int lane, const UnitCoord& c, const KParams& p,
+                                                const OutTargets& outs, uint32_t bad) {
+  constexpr int CPR = TT / S;                     // this rank's columns
+  constexpr int CPW = (CPR + 3) / 4;              // per warp
+  constexpr int BATCH = CPW * S <= 16 ? CPW : 16 / S;
+  const uint32_t my_rank = ptx::cluster_ctarank();
+  const int col0 = (int)my_rank * CPR;
+  const uint32_t rbase = ring + (uint32_t)lane * 16u;
+  const int n = c.wi * 128 + 4 * lane;
+#pragma unroll
+  for (int c0 = 0; c0 < CPW; c0 += BATCH) {
+    float4 x[BATCH][S];
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) {
+      const int cl = pw + 4 * (c0 + i);
+#pragma unroll
+      for (int s = 0; s < S; ++s) {
+        x[i][s] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (cl < CPR) x[i][s] = ptx::ld_rank_f32x4(rbase + (uint32_t)(col0 + cl) * 512u, s, my_rank);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) {
+      const int cl = pw + 4 * (c0 + i);
+      float4 v = x[i][0];
+#pragma unroll
+      for (int s = 1; s < S; ++s) {
+        v.x += x[i][s].x;
+        v.y += x[i][s].y;
+        v.z += x[i][s].z;
+        v.w += x[i][s].w;
+      }
+      const int m = c.ti * TT + col0 + cl;
+      if (cl < CPR && m < p.M && bad == 0) {
+        __nv_bfloat162 b0 = __floats2bfloat162_rn(v.x, v.y), b1 = __floats2bfloat162_rn(v.z, v.w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&b0);
+        o.y = *reinterpret_cast<uint32_t*>(&b1);
+        for (int t = 0; t < outs.n; ++t)
+          *reinterpret_cast<uint2*>(outs.ptr[t] + (long long)m * p.ldc + n) = o;
+      }
+    }
+  }
+}
+
 // SPLITK: 0 = one unit per tile, 1 = split-K through the workspace, 2 = through a cluster.
 template <int TT, int SPLITK = 0>
 __global__ void __launch_bounds__(MxsTraits<TT>::THREADS, 1)
@@ -965,7 +1015,6 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
     ptx::cluster_sync_all();             // every CTA's partial is in its shared memory
     if (warp >= 6 && blockIdx.x < p.num_units) {
       const UnitCoord c = decode_unit(blockIdx.x, p);
-      const int row = (warp & 3) * 32 + lane;
       uint32_t bad = 0;
       {
         const uint32_t abort_addr = ptx::smem_u32(&ctl->abort);
@@ -973,33 +1022,10 @@ fp8mm_mxs_kernel(const __grid_constant__ CUtensorMap tm_tok, const __grid_consta
         for (int s = 0; s < 8; ++s)
           if (s < p.split) bad |= ptx::ld_cluster_u32(ptx::map_to_cta(abort_addr, s));
       }
-      const int cpr = TT / p.split;
-      const int col0 = (int)ptx::cluster_ctarank() * cpr;
-      const uint32_t rbase = ring + (uint32_t)row * 4u;
-      const int n = c.wi * 128 + row;
-      for (int j0 = 0; j0 < cpr; j0 += 4) {
-        float x[4][8];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-#pragma unroll
-          for (int s = 0; s < 8; ++s) {
-            x[u][s] = 0.f;
-            if (s < p.split && j0 + u < cpr)
-              x[u][s] = ptx::ld_cluster_f32(ptx::map_to_cta(rbase + (uint32_t)(col0 + j0 + u) * 512u, s));
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          float v = x[u][0];
-#pragma unroll
-          for (int s = 1; s < 8; ++s)
-            if (s < p.split) v += x[u][s];
-          const int m = c.ti * TT + col0 + j0 + u;
-          if (j0 + u < cpr && m < p.M && bad == 0) {
-            const __nv_bfloat16 b = __float2bfloat16_rn(v);
-            for (int t = 0; t < outs.n; ++t) outs.ptr[t][(long long)m * p.ldc + n] = b;
-          }
-        }
+      switch (p.split) {
+        case 2: mxs_reduce_cols<TT, 2>(ring, warp & 3, lane, c, p, outs, bad); break;
+        case 4: mxs_reduce_cols<TT, 4>(ring, warp & 3, lane, c, p, outs, bad); break;
+        default: mxs_reduce_cols<TT, 8>(ring, warp & 3, lane, c, p, outs, bad); break;
       }
     }
     ptx::cluster_sync_all();             // no rank reads this CTA's shared memory any more

@@ -262,6 +262,20 @@ __device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t cluster_addr) {   //
                : "memory");
   return v;
 }
+// 16 bytes at shared-memory offset `addr` of CTA `rank` of the cluster.  The CTA's own copy is read as plain
+// shared memory: loads through the cluster window run at ~14 bytes per clock and SM, whichever CTA they name.
+__device__ __forceinline__ float4 ld_rank_f32x4(uint32_t addr, uint32_t rank, uint32_t my_rank) {
+  float4 v;
+  if (rank == my_rank) {
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(addr)
+                 : "memory");
+  } else {
+    v = ld_cluster_f32x4(map_to_cta(addr, rank));
+  }
+  return v;
+}
 
 // Named barrier among a subset of the CTA's warps.
 __device__ __forceinline__ void bar_sync(uint32_t id, uint32_t nthreads) {

@@ -101,6 +101,19 @@ def _mx_cost(m, n, k, tile, sms=148):
     return once + -(-units // sms) * (max(1, k // 128) * period + drain)
 
 
+def _gemv_block_t(m, n, k):
+    """Tokens per pass of the decode kernel (1, 2 or 4; every pass of ceil(m / that) streams the weights again,
+    from L2, with its own CTAs): the smallest that keeps the row-passes under ~4700 and their work under
+    ~8.5 M multiply-adds x K, which is where the tuned tables of both profiles change over (512 x 3072: one
+    token per pass up to 5 tokens, two from 6; 2048 x 512: 1 / 2 / 4 from 1 / 3 / 5 tokens; 3072 x 256 and
+    3072 x 2048: two tokens in one pass)."""
+    for bt in (1, 2, 4):
+        passes = -(-m // bt)
+        if passes == 1 or (n * passes <= 4700 and n * passes * k <= 8.5e6):
+            return bt
+    return 4
+
+
 def _gemv_wins(m, n, k):
     """The decode kernel against the 16-token swap-AB tile: always for one or two tokens; up to 8 tokens where
     the layer is at most 2048 rows (one wave of the decode kernel's CTAs) and the work, in passes of four
@@ -111,26 +124,47 @@ def _gemv_wins(m, n, k):
     return m <= GEMV_MAX_TOKENS_SHORT and n <= 2048 and 4 * -(-m // 4) * n * k <= 17e6
 
 
-def _mxs_tile(m, n, k=2048, sms=148):
-    """Token tile (16..128) of the swap-AB block-scaled kernel: the cheapest by waves of (weight tile, token
-    tile) units over the SMs x K blocks x the time of a K block.  Small tiles spread a narrow layer over more
-    SMs; large ones read the weights fewer times."""
-    return min((16, 32, 64, 128), key=lambda t: (_mxs_cost(m, n, k, t, sms), t))
+_MXS_CLUSTER_MAX_CTAS = {2: 148, 4: 128, 8: 64}     # clusters of 8 need eight free SMs in one GPC
+_MXS_STREAM_BYTES_PER_CLK = 3800.0                   # what all CTAs together pull when every weight tile is read once
+_MXS_REDUCE_BASE = 1300.0                           # cycles: two cluster barriers and the first round trip of the reduction
 
 
-def _mxs_split(m, n, k, t):
-    """Split-K of the swap-AB block-scaled kernel: 8 or 4 CTAs per tile (one cluster, partials added over
-    distributed shared memory) where K is long (24 blocks or more) and the tiles alone would leave most of
-    the GPU idle (tiles x split <= 64).  Measured: 4 x 512 x 3072 4.6 us against 6.0 unsplit, 8 x 2048 x 4096
-    5.9 against 7.4; with 16 K blocks, or more CTAs than that, the clusters' fixed cost (~1 us) eats the gain."""
-    kb = k // 128
+def _mxs_split_cost(m, n, k, t, s):
+    """Cycles of the swap-AB block-scaled kernel with s CTAs per tile in a cluster, or None where that is not
+    offered: one wave of clusters; at least three K blocks per CTA; per K block the longer of the kernel's own
+    period and the CTAs' share of the stream; plus the reduction over distributed shared memory, which grows
+    with the token tile (~14 bytes per clock and SM)."""
+    kb = max(1, k // 128)
     units = (n // 128) * -(-m // t)
-    if kb < 24:
-        return 1
-    for s in (8, 4):
-        if kb % s == 0 and units * s <= 64:
-            return s
-    return 1
+    if kb % s or kb // s < 3 or units * s > _MXS_CLUSTER_MAX_CTAS[s]:
+        return None
+    period = max(_MXS_PERIOD[t], units * s * 128.0 * (128 + t) / _MXS_STREAM_BYTES_PER_CLK)
+    return (kb // s) * period + 24.0 * t + 300.0 + _MXS_REDUCE_BASE + 40.0 * t
+
+
+def _mxs_choice(m, n, k, sms=148):
+    """(cycles, token tile, split) of the swap-AB block-scaled kernel: the cheapest of the token tiles 16..128,
+    each unsplit (waves of (weight tile, token tile) units over the SMs x K blocks x the time of a K block:
+    small tiles spread a narrow layer over more SMs, large ones read the weights fewer times) or split 2, 4 or
+    8 ways along K.  Measured on a B200 (us, best split against unsplit): 4 x 512 x 3072 4.2 / 6.1,
+    8 x 2048 x 4096 4.9 / 7.4, 32 x 2048 x 4096 5.7 / 7.6, 16 x 2048 x 2048 4.3 / 5.1, 16 x 3072 x 2048 4.6 / 5.2;
+    no gain at 64 x 2048 x 2048 (5.5 / 5.2) or 16 x 5120 x 3072 (6.5 / 6.4): enough tiles already."""
+    best = None
+    for t in (16, 32, 64, 128):
+        cands = [(_mxs_cost(m, n, k, t, sms), t, 1)]
+        for s in (2, 4, 8):
+            c = _mxs_split_cost(m, n, k, t, s)
+            if c is not None:
+                cands.append((1.1 * c, t, s))       # a split has to promise 10 % to be taken
+        for cand in cands:
+            if best is None or cand < best:
+                best = cand
+    return best
+
+
+def _mxs_tile(m, n, k=2048, sms=148):
+    """Token tile (16..128) of the unsplit swap-AB block-scaled kernel by the cost model of `_mxs_choice`."""
+    return min((16, 32, 64, 128), key=lambda t: (_mxs_cost(m, n, k, t, sms), t))
 
 
 def _mx_tile(m, n, k=2048, sms=148):
@@ -144,12 +178,11 @@ def plan_ue8m0(m, n, k, sms=148):
     models above (the swap-AB tiles win wherever the token-major ones would leave most SMs without a tile:
     up to ~1000 tokens on layers of a few thousand rows)."""
     if _gemv_wins(m, n, k):
-        return "gemv", {"BLOCK_T": 1 if m <= 2 else 4, "SCALES_UE8M0": True}
-    t = _mxs_tile(m, n, k, sms)
+        return "gemv", {"BLOCK_T": _gemv_block_t(m, n, k), "SCALES_UE8M0": True}
+    cost, t, split = _mxs_choice(m, n, k, sms)
     tile = _mx_tile(m, n, k, sms)
-    if _mxs_cost(m, n, k, t, sms) <= _mx_cost(m, n, k, tile, sms):
-        return "umma_mx", {"BLOCK_T": t, "BLOCK_W": 128, "NUM_STAGES": 4, "GROUP_SIZE_M": 1,
-                           "SPLIT": _mxs_split(m, n, k, t)}
+    if cost <= _mx_cost(m, n, k, tile, sms):
+        return "umma_mx", {"BLOCK_T": t, "BLOCK_W": 128, "NUM_STAGES": 4, "GROUP_SIZE_M": 1, "SPLIT": split}
     return "umma_mx", {"BLOCK_T": tile[0], "BLOCK_W": tile[1]}
 
 
