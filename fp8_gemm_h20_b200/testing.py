@@ -31,13 +31,8 @@ def quantize_weights(w, floor=1e-10):
     return q, scale.contiguous()
 
 
-def make_problem(m, n, k, seed=0, mode="cfg0", device="cpu"):
-    """(A, B, As, Bs) on `device`, generated on the CPU from `seed`.
-
-    modes: "cfg0"  X~N(0,1) as bf16 with 1% of the K channels x20, W~N(0,0.02)
-           "normal"/"outlier"/"skew"/"zero"  the four distributions of scripts/validate.py:21-25
-           (X~N(0,1), W~0.05 N(0,1); every 127th channel x100; weight row blocks x logspace(-3,1);
-           all-zero activations), scale floor 1e-6 as there."""
+def _raw_problem(m, n, k, seed, mode):
+    """Activations x[m,k], weights w[n,k] as float32 and the scale floor of one test problem (see make_problem)."""
     import torch
     gen = torch.Generator().manual_seed(int(seed))
     x = torch.randn(m, k, generator=gen)
@@ -60,28 +55,34 @@ def make_problem(m, n, k, seed=0, mode="cfg0", device="cpu"):
             x.zero_()
         elif mode != "normal":
             raise ValueError(mode)
+    return x, w, floor
+
+
+def make_problem(m, n, k, seed=0, mode="cfg0", device="cpu"):
+    """(A, B, As, Bs) on `device`, generated on the CPU from `seed`.
+
+    modes: "cfg0"  X~N(0,1) as bf16 with 1% of the K channels x20, W~N(0,0.02)
+           "normal"/"outlier"/"skew"/"zero"  the four distributions of scripts/validate.py:21-25
+           (X~N(0,1), W~0.05 N(0,1); every 127th channel x100; weight row blocks x logspace(-3,1);
+           all-zero activations), scale floor 1e-6 as there."""
+    x, w, floor = _raw_problem(m, n, k, seed, mode)
     A, As = quantize_activations(x, floor)
     B, Bs = quantize_weights(w, floor)
     return tuple(t.to(device) for t in (A, B, As, Bs))
 
 
-def make_problem_ue8m0(m, n, k, seed=0, device="cpu"):
-    """(A, B, As_u8, Bs_u8, As, Bs): the "cfg0" problem quantised with power-of-two scales (each block's
-    scale rounded UP to 2^e, as UE8M0 checkpoints are made); As_u8/Bs_u8 hold e + 127, As/Bs the same
-    scales as float32 for the references."""
+def make_problem_ue8m0(m, n, k, seed=0, device="cpu", mode="cfg0"):
+    """(A, B, As_u8, Bs_u8, As, Bs): the problem of `make_problem` (same modes) quantised with power-of-two
+    scales (each block's scale rounded UP to 2^e, as UE8M0 checkpoints are made); As_u8/Bs_u8 hold e + 127,
+    As/Bs the same scales as float32 for the references."""
     import torch
-    gen = torch.Generator().manual_seed(int(seed))
-    x = torch.randn(m, k, generator=gen)
-    w = torch.randn(n, k, generator=gen) * 0.02
-    idx = torch.randperm(k, generator=gen)[:max(1, math.ceil(0.01 * k))]
-    x[:, idx] *= 20.0
-    x = x.to(torch.bfloat16).float()
+    x, w, floor = _raw_problem(m, n, k, seed, mode)
     xa = x.view(m, k // 128, 128)
-    ea = torch.ceil(torch.log2(xa.abs().amax(-1).clamp_min(1e-10) / FP8_MAX)).clamp(-127, 127)
+    ea = torch.ceil(torch.log2(xa.abs().amax(-1).clamp_min(floor) / FP8_MAX)).clamp(-127, 127)
     As = torch.exp2(ea)
     A = (xa / As[..., None]).clamp(-FP8_MAX, FP8_MAX).reshape(m, k).to(torch.float8_e4m3fn)
     wb = w.view(n // 128, 128, k // 128, 128)
-    eb = torch.ceil(torch.log2(wb.abs().amax((1, 3)).clamp_min(1e-10) / FP8_MAX)).clamp(-127, 127)
+    eb = torch.ceil(torch.log2(wb.abs().amax((1, 3)).clamp_min(floor) / FP8_MAX)).clamp(-127, 127)
     Bs = torch.exp2(eb)
     B = (wb / Bs[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).reshape(n, k).to(torch.float8_e4m3fn)
     As_u8 = (ea + 127).to(torch.uint8)

@@ -3,7 +3,7 @@ profile - the B200 counterpart of the reference's scripts/validate.py (:39-118 t
 same options, checks and JSON report:
 
     python -m fp8_gemm_h20_b200.validate --profile 35b_tp1 --output report.json
-                                         [--reference DIR] [--timing] [--quick]
+                                         [--reference DIR] [--timing] [--quick] [--ue8m0]
 
 * accuracy: every (N,K) of the profile x the reference's M lists x {normal, outlier, skew, zero}:
   finite and max|C-ref|/max|ref| < 1e-2 against dequantise -> FP32 matmul on the GPU;
@@ -11,7 +11,9 @@ same options, checks and JSON report:
   root has a `dispatch.py` with `matmul(A,B,As,Bs)`); every output must be bit-identical to it;
 * graphs: one representative problem per kernel path, captured on two streams and replayed 100x;
 * strided scales: both scale tensors as transposed-contiguous views;
-* --timing: median microseconds under graph replay for M in {1,37,64,128,200,511,512,8192}.
+* --timing: median microseconds under graph replay for M in {1,37,64,128,200,511,512,8192};
+* --ue8m0: the same run through `matmul_ue8m0`: the same data quantised with power-of-two scales (exponent
+  bytes), the decode / block-scaled kernels chosen by `quant.plan_ue8m0` instead of the profile's table.
 Use CUDA_VISIBLE_DEVICES to pick the GPU.
 """
 import argparse
@@ -36,7 +38,8 @@ def summary_markdown(report, ms, argv):
     worst = max(acc, key=lambda r: r["error"])
     by_mode = {mode: max(r["error"] for r in acc if r["mode"] == mode) for mode in MODES}
     shapes = sorted({(r["N"], r["K"]) for r in acc})
-    lines = [f"# Acceptance run: profile `{report['profile']}` on {report['device']}", "",
+    kind = " with power-of-two (UE8M0) scales through `matmul_ue8m0`" if report.get("scales") == "ue8m0" else ""
+    lines = [f"# Acceptance run: profile `{report['profile']}`{kind} on {report['device']}", "",
              f"Command: `python -m fp8_gemm_h20_b200.validate {' '.join(argv)}`", "",
              f"* accuracy: **{len(acc)} cases** = {len(shapes)} shapes x {len(ms)} token counts x {len(MODES)} "
              f"distributions, every output finite and max|C-ref|/max|ref| < 1e-2 against dequantise -> FP32 matmul "
@@ -65,13 +68,16 @@ def main(argv=None):
     ap.add_argument("--quick", action="store_true", help="five token counts per shape instead of the full list")
     ap.add_argument("--rounds", type=int, default=5)
     ap.add_argument("--summary-md", help="also write a short markdown summary of the run to this path")
+    ap.add_argument("--ue8m0", action="store_true",
+                    help="power-of-two scales as exponent bytes through matmul_ue8m0 (no table involved)")
     a = ap.parse_args(argv)
 
     import torch
     from . import matmul, select
     from .config import get_profile
-    from .testing import make_problem, reference_fp32, rel_error
+    from .testing import make_problem, make_problem_ue8m0, reference_fp32, rel_error
     from .tune import bench_us
+    from . import quant
 
     torch.backends.cuda.matmul.allow_tf32 = False
     prior = None
@@ -81,17 +87,36 @@ def main(argv=None):
     config = get_profile(a.profile)
     ms = MS_QUICK if a.quick else (MS_35 if "35b" in a.profile else MS_122)
     report = dict(profile=a.profile, device=torch.cuda.get_device_name(), torch=torch.__version__,
-                  accuracy=[], timing=[], graphs=[], strided_scales=[])
+                  scales="ue8m0" if a.ue8m0 else "fp32", accuracy=[], timing=[], graphs=[], strided_scales=[])
 
     def problem(m, n, k, mode, seed_shift=0):
-        return tuple(t.cuda() for t in make_problem(m, n, k, seed=m + n + k + 113 + seed_shift, mode=mode))
+        seed = m + n + k + 113 + seed_shift
+        if not a.ue8m0:
+            return tuple(t.cuda() for t in make_problem(m, n, k, seed=seed, mode=mode))
+        return tuple(t.cuda() for t in make_problem_ue8m0(m, n, k, seed=seed, mode=mode)[:4])
+
+    if a.ue8m0:
+        if a.reference:
+            raise SystemExit("--reference compares table kernels; it does not go with --ue8m0")
+        plain_reference = reference_fp32
+
+        def reference_fp32(A, B, Au, Bu):        # noqa: F811  (the scales as floats: exact, they are powers of two)
+            As, Bs = (torch.exp2(t.float() - 127.0) for t in (Au, Bu))
+            return plain_reference(A, B, As, Bs)
+
+        def matmul(A, B, Au, Bu, profile=None):  # noqa: F811
+            return quant.matmul_ue8m0(A, B, Au, Bu)
 
     reps = {}
     for nk in config["entries"]:
         n, k = map(int, nk.split(","))
         for m in ms:
-            entry, _ = select(a.profile, m, n, k)
-            c = entry["config"]
+            if a.ue8m0:
+                impl, c = quant.plan_ue8m0(m, n, k)
+                entry = {"impl": impl, "config": c}
+            else:
+                entry, _ = select(a.profile, m, n, k)
+                c = entry["config"]
             reps.setdefault((entry["impl"], c.get("BLOCK_T"), c.get("BLOCK_W"), c.get("SPLIT", 1) > 1, k), (m, n, k))
             for mode in MODES:
                 args = problem(m, n, k, mode)
