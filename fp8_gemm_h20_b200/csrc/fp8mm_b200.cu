@@ -109,6 +109,10 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
       g->tiles = g->t_tiles * g->w_tiles;
       g->kb_total = K / 128;
       g->kg = g->tt <= 64 ? 4 : 2;           // K blocks per ring slot = issuing threads (MxsTraits<TT>::NI)
+      // FP8MM_FLAG_K_PAIRS on unsplit tiles: the half-size form (half the issuing threads, ring slot and tensor
+      // memory), of which two CTAs share an SM
+      const bool half_form = (c->flags & FP8MM_FLAG_K_PAIRS) && !(c->split > 1) && g->tt <= 64;
+      if (half_form) g->kg = 2;
       // split-K: a split that does not divide the K-block count runs unsplit, like the table kernels'
       g->split = (c->split > 1 && g->kb_total % c->split == 0 && g->tiles <= kMaxSplitTiles) ? c->split : 1;
       g->kbn = g->kb_total / g->split;
@@ -130,7 +134,8 @@ int make_geometry(int M, int N, int K, const fp8mm_cfg* c, Geometry* g) {
       g->counter_bytes = ws_split ? kCounterBytes : 0;
       g->partial_bytes = ws_split ? (size_t)g->tiles * g->split * g->tt * 128 * sizeof(float) : 0;
       size_t smem = fixed + (size_t)stages * stage_bytes;
-      const size_t tmem_cols = g->tt <= 16 ? 128 : (g->tt <= 32 ? 256 : 512);   // MxsTraits<TT>::TMEM_COLS
+      size_t tmem_cols = g->tt <= 16 ? 128 : (g->tt <= 32 ? 256 : 512);   // MxsTraits<TT, NI>::TMEM_COLS
+      if (half_form) tmem_cols = g->tt <= 16 ? 64 : (g->tt <= 32 ? 128 : 256);
       const size_t floor_smem = tmem_cols * 456 - 1024;     // shared-memory share >= TMEM share (see below)
       g->smem = smem < floor_smem ? floor_smem : smem;
       return FP8MM_OK;
@@ -382,7 +387,7 @@ int make_output_map(void* c, int m, int n, long long ldc, CUtensorMap* out, bool
 // ----------------------------------------------------------------- launch
 struct DeviceInfo {
   int sms = 0;
-  bool attr_set[54] = {};     // 0..35 tile kernels, 39 CTA-pair kernel, 40/41 block-scaled (UE8M0) kernels
+  bool attr_set[57] = {};     // 0..35 tile kernels, 39 CTA-pair kernel, 40/41 block-scaled (UE8M0) kernels
   // cluster split-K kernels: can a cluster of 2 / 4 / 8 such CTAs be placed at all?  0 = not asked
   // yet, 1 = yes, 2 = no (an SM-limited context, MPS or a green context can say no)
   unsigned char cluster_ok[54][4] = {};
@@ -816,6 +821,11 @@ static int gemm_impl(const fp8mm_args* a, const fp8mm_cfg* cfg, void* workspace,
       case 64: kern[0] = fp8mm_mxs_kernel<64, 0>; kern[1] = fp8mm_mxs_kernel<64, 1>; kern[2] = fp8mm_mxs_kernel<64, 2>; slot = 44; break;
       case 128: kern[0] = fp8mm_mxs_kernel<128, 0>; kern[1] = fp8mm_mxs_kernel<128, 1>; kern[2] = fp8mm_mxs_kernel<128, 2>; slot = 45; break;
       default: return FP8MM_E_CONFIG;
+    }
+    if (g.split == 1 && g.kg == 2 && g.tt <= 64) {        // slots 54..56: the half-size form, two CTAs per SM
+      PlainKernel k2 = g.tt == 16 ? fp8mm_mxs_kernel<16, 0, 2>
+                                  : (g.tt == 32 ? fp8mm_mxs_kernel<32, 0, 2> : fp8mm_mxs_kernel<64, 0, 2>);
+      return launch_plain(k2, slot + 12, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
     }
     if (g.split == 1) return launch_plain(kern[0], slot, dev, g, tm_tok, tm_wgt, outs, p, grid, stream);
     if (g.cluster) {

@@ -48,6 +48,7 @@ def make_cfg(impl, config):
                     stages=int(c["NUM_STAGES"]), split=int(c["SPLIT"]),
                     group_m=int(c["GROUP_SIZE_M"]), max_ctas=int(c.get("MAX_CTAS", 0)),
                     flags=(1 if c.get("SPLIT_VIA_WORKSPACE") else 0) | _k_group_flag(int(c.get("K_GROUP", 1)))
+                    | (2 if c.get("HALF_FORM") else 0)
                     | (4 if c.get("SCALES_UE8M0") else 0) | (8 if c.get("ACT_SCALES_F32") else 0))
 
 

@@ -83,7 +83,7 @@ GEMV_MAX_TOKENS_SHORT = 8   # up to here on narrow layers with little work (_gem
 # tensor-core instructions up to 64 tokens, by the copies at 128).  Token-major tiles: one K block (bound by
 # shared-memory bandwidth), the accumulator drain per tile, and what a launch pays once (set-up, first
 # copies in flight, last drain).
-_MXS_PERIOD = {16: 300.0, 32: 315.0, 64: 380.0, 128: 750.0}
+_MXS_PERIOD = {16: 300.0, 32: 315.0, 64: 380.0, 128: 880.0}
 _MX_TILES = {(128, 256): (790.0, 1500.0, 4000.0), (256, 224): (1200.0, 2600.0, 5000.0)}
 
 
@@ -142,20 +142,39 @@ def _mxs_split_cost(m, n, k, t, s):
     return (kb // s) * period + 24.0 * t + 300.0 + _MXS_REDUCE_BASE + 40.0 * t
 
 
+# The half-size form of the 32- and 64-token tiles (two issuing threads, two CTAs per SM): cycles of a K block
+# for each of the two CTAs of an SM, and what their unit pays on top of the accumulator drain.
+_MXS_HALF = {32: (600.0, 0.0), 64: (720.0, 0.0)}
+
+
+def _mxs_half_cost(m, n, k, t, sms=148):
+    """Cycles with two CTAs per SM, or None where that cannot pay: with no more units than SMs every CTA has an
+    SM to itself anyway and four issuing threads are faster than two (timed: 384 x 3072 x 2048, 144 units, 7.3 us
+    against 7.0; 256 x 9216 x 2048, 288 units, 9.8 against 11.6)."""
+    units = (n // 128) * -(-m // t)
+    if t not in _MXS_HALF or units <= sms:
+        return None
+    period, extra = _MXS_HALF[t]
+    return -(-units // (2 * sms)) * (max(1, k // 128) * period + 24.0 * t + 300.0 + extra)
+
+
 def _mxs_choice(m, n, k, sms=148):
-    """(cycles, token tile, split) of the swap-AB block-scaled kernel: the cheapest of the token tiles 16..128,
-    each unsplit (waves of (weight tile, token tile) units over the SMs x K blocks x the time of a K block:
+    """(cycles, token tile, split, half-size form) of the swap-AB block-scaled kernel: the cheapest of the token
+    tiles 16..128, each unsplit (waves of (weight tile, token tile) units over the SMs x K blocks x the time of a K block:
     small tiles spread a narrow layer over more SMs, large ones read the weights fewer times) or split 2, 4 or
-    8 ways along K.  Measured on a B200 (us, best split against unsplit): 4 x 512 x 3072 4.2 / 6.1,
+    8 ways along K, or in its half-size form with two CTAs per SM.  Measured on a B200 (us, best split against unsplit): 4 x 512 x 3072 4.2 / 6.1,
     8 x 2048 x 4096 4.9 / 7.4, 32 x 2048 x 4096 5.7 / 7.6, 16 x 2048 x 2048 4.3 / 5.1, 16 x 3072 x 2048 4.6 / 5.2;
     no gain at 64 x 2048 x 2048 (5.5 / 5.2) or 16 x 5120 x 3072 (6.5 / 6.4): enough tiles already."""
     best = None
     for t in (16, 32, 64, 128):
-        cands = [(_mxs_cost(m, n, k, t, sms), t, 1)]
+        cands = [(_mxs_cost(m, n, k, t, sms), t, 1, False)]
         for s in (2, 4, 8):
             c = _mxs_split_cost(m, n, k, t, s)
             if c is not None:
-                cands.append((1.1 * c, t, s))       # a split has to promise 10 % to be taken
+                cands.append((1.1 * c, t, s, False))       # a split has to promise 10 % to be taken
+        c = _mxs_half_cost(m, n, k, t, sms)
+        if c is not None:
+            cands.append((c, t, 1, True))
         for cand in cands:
             if best is None or cand < best:
                 best = cand
@@ -179,10 +198,13 @@ def plan_ue8m0(m, n, k, sms=148):
     up to ~1000 tokens on layers of a few thousand rows)."""
     if _gemv_wins(m, n, k):
         return "gemv", {"BLOCK_T": _gemv_block_t(m, n, k), "SCALES_UE8M0": True}
-    cost, t, split = _mxs_choice(m, n, k, sms)
+    cost, t, split, half = _mxs_choice(m, n, k, sms)
     tile = _mx_tile(m, n, k, sms)
     if cost <= _mx_cost(m, n, k, tile, sms):
-        return "umma_mx", {"BLOCK_T": t, "BLOCK_W": 128, "NUM_STAGES": 4, "GROUP_SIZE_M": 1, "SPLIT": split}
+        conf = {"BLOCK_T": t, "BLOCK_W": 128, "NUM_STAGES": 2 if half else 4, "GROUP_SIZE_M": 1, "SPLIT": split}
+        if half:
+            conf["HALF_FORM"] = True
+        return "umma_mx", conf
     return "umma_mx", {"BLOCK_T": tile[0], "BLOCK_W": tile[1]}
 
 

@@ -63,7 +63,11 @@ extern "C" {
 #define FP8MM_FLAG_WORKSPACE_SPLIT 1
 /* cfg.flags: two K blocks per shared-memory ring slot, fetched by one 3-D TMA copy per operand
  * (swap-AB tiles of 16..64 tokens; needs an even number of K blocks per split, otherwise ignored).
- * Halves the per-K-block work of the single TMA-issuing thread, which paces small-M calls. */
+ * Halves the per-K-block work of the single TMA-issuing thread, which paces small-M calls.
+ * With FP8MM_IMPL_UMMA_MX swap-AB tiles of 16..64 tokens (unsplit): the half-size form, two K blocks per slot
+ * and two MMA-issuing threads instead of four, half the tensor memory, so that two CTAs share an SM; pays
+ * where the work units outnumber the SMs.  Accumulation order differs from the full-size form (two partial
+ * sums instead of four), the result stays within the same tolerance. */
 #define FP8MM_FLAG_K_PAIRS 2
 /* cfg.flags bits 8..11: K blocks per ring slot, 2..8 (table key K_GROUP); generalises FP8MM_FLAG_K_PAIRS.
  * Needs the count to divide the K blocks of every split and two such slots to fit in shared
