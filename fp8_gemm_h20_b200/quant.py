@@ -76,8 +76,7 @@ def ue8m0_bytes(scales):
     raise ValueError("UE8M0 scales come as uint8 exponents, int32 words of four exponents, or float32 powers of two")
 
 
-GEMV_MAX_TOKENS = 2         # up to here always the decode kernel (it reads the exponent bytes itself);
-GEMV_MAX_TOKENS_SHORT = 8   # up to here on narrow layers with little work (_gemv_wins)
+GEMV_MAX_TOKENS_SHORT = 8   # the decode kernel (it reads the exponent bytes itself) is considered up to here (_gemv_wins)
 
 # Cycles measured on a B200.  Swap-AB block-scaled tiles by token tile: one K block (bound by the issue of
 # tensor-core instructions up to 64 tokens, by the copies at 128).  Token-major tiles: one K block (bound by
@@ -115,13 +114,18 @@ def _gemv_block_t(m, n, k):
 
 
 def _gemv_wins(m, n, k):
-    """The decode kernel against the 16-token swap-AB tile: always for one or two tokens; up to 8 tokens where
-    the layer is at most 2048 rows (one wave of the decode kernel's CTAs) and the work, in passes of four
-    tokens, stays under what the tile kernel needs for its K blocks (timed: 4 x 2048 x 2048 4.0 us against
-    5.3, 8 x 1024 x 2048 3.8 against 5.0, but 8 x 2048 x 2048 6.9 against 5.0 and 4 x 3072 x 2048 7.3 against 5.3)."""
-    if m <= GEMV_MAX_TOKENS:
+    """The decode kernel against the 16-token swap-AB tile, from timings of both on a B200: always for one
+    token; for two up to ~15 M weights (2 x 4608 x 3072 5.5 us against 5.8, but 2 x 9216 x 2048 6.4 against 5.3);
+    up to 8 tokens where the layer is at most 2048 rows (one wave of the decode kernel's CTAs; 4096 rows while
+    one pass of four tokens does it) and the work, in passes of four tokens, stays under what the tile kernel
+    needs for its K blocks (4 x 2048 x 2048 4.0 us against 5.3, 8 x 1024 x 2048 3.3 against 4.2, 4 x 3072 x 256 2.4
+    against 3.0, but 8 x 2048 x 2048 6.9 against 5.0 and 4 x 3072 x 2048 6.6 against 4.5)."""
+    if m == 1:
         return True
-    return m <= GEMV_MAX_TOKENS_SHORT and n <= 2048 and 4 * -(-m // 4) * n * k <= 17e6
+    if m == 2:
+        return n * k <= 15e6
+    rows_max = 4096 if m <= 4 else 2048
+    return m <= GEMV_MAX_TOKENS_SHORT and n <= rows_max and 4 * -(-m // 4) * n * k <= 17e6
 
 
 _MXS_CLUSTER_MAX_CTAS = {2: 148, 4: 128, 8: 64}     # clusters of 8 need eight free SMs in one GPC
@@ -192,7 +196,7 @@ def _mx_tile(m, n, k=2048, sms=148):
 
 
 def plan_ue8m0(m, n, k, sms=148):
-    """(impl, config) of `matmul_ue8m0` for one problem: the decode kernel for one or two tokens (up to 8
+    """(impl, config) of `matmul_ue8m0` for one problem: the decode kernel for one token, for two on all but the largest layers (up to 8
     where the layer is narrow or K short), else the cheaper of the swap-AB and the token-major block-scaled tiles by the cost
     models above (the swap-AB tiles win wherever the token-major ones would leave most SMs without a tile:
     up to ~1000 tokens on layers of a few thousand rows)."""
@@ -212,7 +216,7 @@ def matmul_ue8m0(A, B, As, Bs, *, profile="35b_tp1"):
     """`matmul` for power-of-two scales: A[M,K], B[N,K] float8_e4m3fn, As[M,K/128] and Bs[N/128,K/128]
     in any of the forms `ue8m0_bytes` takes -> bfloat16 C[M,N].
 
-    The scales stay bytes all the way: the decode kernel reads them for one or two tokens, the swap-AB
+    The scales stay bytes all the way: the decode kernel reads them for a few tokens, the swap-AB
     and token-major block-scaled kernels hand them to the tensor cores (`umma_mx`, tcgen05.mma
     kind::mxf8f6f4.block_scale); `plan_ue8m0` picks by measured cost models.  No shape table is involved, so
     any N and K that are multiples of 128 work; `profile` is accepted for symmetry with `matmul`."""
